@@ -2,7 +2,9 @@
  * stream: one RMS norm per layer feeding mixer and feed-forward side by side (softmax attention with a sink whose values
  * are its keys, selective scans, gated delta rule layers, squared-ReLU feed-forward), and norm - sublayer - norm blocks
  * with element-wise tanh norms and per-channel layer scales (scalar-decay state-space recurrence, attention over a shared
- * low-rank latent with a rotated key part, gated linear recurrence, routed gated experts).
+ * low-rank latent with a rotated key part, gated linear recurrence, routed gated experts), and blocks whose sublayers read
+ * the stream itself and are RMS-normed on the way back (attention over a sliding window plus pooled blocks with rotated
+ * values, matrix memory with capped exponential gates, gated dense feed-forward, routed plain experts beside a shared one).
  *
  * Same conventions as jacobi_b200.h: every function returns 0 or a negative status, hy_last_error(h) gives the text,
  * plain pointers and sizes only, host buffers are caller-owned, device memory belongs to the handle, one host thread per
@@ -26,14 +28,23 @@ typedef struct hy_engine* hy_handle;
 
 typedef enum { HY_OK = 0, HY_ERR_INVALID = -1, HY_ERR_CUDA = -2, HY_ERR_CAPACITY = -3, HY_ERR_UNSUPPORTED = -4 } hy_status;
 typedef enum { HY_DTYPE_BF16 = 0, HY_DTYPE_F32 = 1, HY_DTYPE_F16 = 2, HY_DTYPE_I32 = 3 } hy_dtype;
-typedef enum { HY_MIX_ATTN_SCAN = 0, HY_MIX_DELTA = 1, HY_MIX_SSD = 2, HY_MIX_LATENT = 3, HY_MIX_GLR = 4 } hy_mixer_kind;
-typedef enum { HY_FF_NONE = 0, HY_FF_RELU2 = 1, HY_FF_ROUTED = 2 } hy_ff_kind;
-/* norm of the residual stream: RMS with a weight stored as an offset from one | tanh(alpha x) w + b (no statistics) */
-typedef enum { HY_NORM_RMS_OFFSET = 0, HY_NORM_TANH = 1 } hy_norm_kind;
+typedef enum { HY_MIX_ATTN_SCAN = 0, HY_MIX_DELTA = 1, HY_MIX_SSD = 2, HY_MIX_LATENT = 3, HY_MIX_GLR = 4, HY_MIX_WINDOW = 5,
+               HY_MIX_MLSTM = 6 } hy_mixer_kind;
+/* HY_FF_GATED: down(act(gate x) * (up x)), act = hy_act_kind in ff_act */
+typedef enum { HY_FF_NONE = 0, HY_FF_RELU2 = 1, HY_FF_ROUTED = 2, HY_FF_GATED = 3 } hy_ff_kind;
+typedef enum { HY_ACT_SILU = 0, HY_ACT_GELU_TANH = 1, HY_ACT_GELU_ERF = 2 } hy_act_kind;
+/* how a routed feed-forward scores its experts: sigmoid scores, group-limited choice, weights normalised to x_scale |
+ * the largest logits (plus a bias per expert), weights = softmax over the chosen logits alone */
+typedef enum { HY_ROUTE_SIGMOID_GROUPS = 0, HY_ROUTE_TOP_SOFTMAX = 1 } hy_route_kind;
+/* norm of the residual stream: RMS with a weight stored as an offset from one | tanh(alpha x) w + b (no statistics) |
+ * RMS with a plain weight */
+typedef enum { HY_NORM_RMS_OFFSET = 0, HY_NORM_TANH = 1, HY_NORM_RMS = 2 } hy_norm_kind;
 /* HY_BLOCK_PARALLEL: x += mixer(n(x)) + ff(n(x)), one norm per layer.
  * HY_BLOCK_SANDWICH: x += ls1 * n1b(mixer(n1(x))), then x += ls2 * n2b(ff(n2(x))): a norm on both sides of each sublayer
- * and a per-channel layer scale. */
-typedef enum { HY_BLOCK_PARALLEL = 0, HY_BLOCK_SANDWICH = 1 } hy_block_kind;
+ * and a per-channel layer scale.
+ * HY_BLOCK_POSTNORM: x += ls1 * n1(mixer(x)), then x += ls2 * n2(ff(x)): the sublayers read the stream itself, the norm
+ * (RMS, with statistics over the width) sits on the sublayer's output. */
+typedef enum { HY_BLOCK_PARALLEL = 0, HY_BLOCK_SANDWICH = 1, HY_BLOCK_POSTNORM = 2 } hy_block_kind;
 typedef enum { HY_POS_SINUSOID = 0, HY_POS_NONE = 1 } hy_pos_kind;   /* what is added to the scaled embedding */
 
 typedef struct {
@@ -66,6 +77,20 @@ typedef struct {
    * factor on the normalised weights */
   int32_t x_experts, x_top, x_groups, x_keep;
   float x_scale;
+  /* more of HY_FF_ROUTED: hy_route_kind; experts without a gate (down(act(up x))); hy_act_kind of the experts; size of a
+   * shared expert of the same form that every token uses with weight one (0: none).  ff_act: hy_act_kind of HY_FF_GATED */
+  int32_t x_route, x_plain, x_act, x_shared_ff, ff_act;
+  /* HY_MIX_WINDOW (softmax attention over a sliding window plus one pooled key / value per block of w_pool tokens that
+   * lies wholly before the window): query heads, key/value heads, key size, value size, window length, block length,
+   * rotated dimensions of queries and keys (pairs 2i, 2i + 1; 0: none), values rotated by their own position over all
+   * of w_vdim and the output turned back by the query's (0 / 1), RMS norm per head on queries and keys (0 / 1);
+   * rotation base, score scale */
+  int32_t w_heads, w_kv_heads, w_dim, w_vdim, w_window, w_pool, w_rot_dims, w_rot_values, w_qk_norm;
+  float w_rot_base, w_scale;
+  /* HY_MIX_MLSTM (matrix memory with exponential gates under a running maximum): heads, key size, value size, the cap
+   * c of both gate pre-activations (c tanh(z / c); <= 0: no cap) */
+  int32_t t_heads, t_dim, t_vdim;
+  float t_gate_cap;
 } hy_layer_cfg;
 
 typedef struct {
@@ -73,6 +98,8 @@ typedef struct {
   int32_t dtype;                   /* HY_DTYPE_BF16: bf16 operands, fp32 accumulation / state / residual; HY_DTYPE_F32: all fp32 */
   float emb_scale, logit_scale, norm_eps;
   int32_t norm_kind, block_kind, pos_kind;   /* hy_norm_kind, hy_block_kind, hy_pos_kind */
+  int32_t embed_norm;              /* 1: the embedding passes through the model's norm with the weight "embed.norm" */
+  int32_t tied_head;               /* 1: the output head is the embedding table (no "head" tensor) */
 } hy_model_cfg;
 
 typedef struct {

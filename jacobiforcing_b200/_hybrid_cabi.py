@@ -10,7 +10,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libjf_hybrid.so")
-SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "hy_attn.cuh", "hy_mixers.cuh", "hy_experts.cuh",
+SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "hy_attn.cuh", "hy_mixers.cuh", "hy_experts.cuh", "hy_window.cuh",
                                                         "jf_ptx.cuh")] + [
     os.path.join(ROOT, "include", "jacobi_hybrid.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
@@ -34,13 +34,19 @@ class LayerCfg(C.Structure):
                 [("l_scale", C.c_float), ("r_dims", C.c_int32)] +
                 [(n, C.c_float) for n in ("r_base", "r_factor", "r_original", "r_fast", "r_slow")] +
                 [(n, C.c_int32) for n in ("g_heads", "g_dim", "g_vdim", "x_experts", "x_top", "x_groups", "x_keep")] +
-                [("x_scale", C.c_float)])
+                [("x_scale", C.c_float)] +
+                [(n, C.c_int32) for n in ("x_route", "x_plain", "x_act", "x_shared_ff", "ff_act")] +
+                [(n, C.c_int32) for n in ("w_heads", "w_kv_heads", "w_dim", "w_vdim", "w_window", "w_pool", "w_rot_dims",
+                                          "w_rot_values", "w_qk_norm")] +
+                [("w_rot_base", C.c_float), ("w_scale", C.c_float)] +
+                [(n, C.c_int32) for n in ("t_heads", "t_dim", "t_vdim")] + [("t_gate_cap", C.c_float)])
 
 
 class ModelCfg(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32),
                 ("emb_scale", C.c_float), ("logit_scale", C.c_float), ("norm_eps", C.c_float),
-                ("norm_kind", C.c_int32), ("block_kind", C.c_int32), ("pos_kind", C.c_int32)]
+                ("norm_kind", C.c_int32), ("block_kind", C.c_int32), ("pos_kind", C.c_int32),
+                ("embed_norm", C.c_int32), ("tied_head", C.c_int32)]
 
 
 class RuntimeCfg(C.Structure):

@@ -20,6 +20,7 @@
 #include "hy_attn.cuh"
 #include "hy_mixers.cuh"
 #include "hy_experts.cuh"
+#include "hy_window.cuh"
 
 namespace hy {
 
@@ -64,6 +65,16 @@ struct LayerW {
   void* w_router = nullptr; void* w_router_t = nullptr; void* w_gu = nullptr; void* w_down = nullptr;
   // the same as swizzled tiles per expert for the tensor-core product: gate/up rows alternate in blocks of 16
   void* w_gu_t = nullptr; void* w_down_t = nullptr; size_t gu_t_stride = 0, down_t_stride = 0; int gu_rows = 0;
+  // blocks normed on the sublayer's output: plain RMS weights; router bias; the shared expert; the gated dense feed-forward
+  // ([gate rows | up rows] stacked, and as tiles whose rows alternate 16 gate and 16 up features)
+  float* pn1 = nullptr; float* pn2 = nullptr; float* x_rb = nullptr;
+  void* w_sh_up = nullptr; void* w_sh_up_t = nullptr; void* w_sh_down = nullptr; void* w_sh_down_t = nullptr;
+  void* w_ff_in = nullptr; void* w_ff_in_t = nullptr; int ff_rows = 0; void* w_ff_down = nullptr; void* w_ff_down_t = nullptr;
+  // window attention: query / key norm weights, the values' rotation, value pages, pooled key / value pages
+  float* w_qn = nullptr; float* w_kn = nullptr; Rotation rot_v{};
+  void* cache_v = nullptr; void* pool_k = nullptr; void* pool_v = nullptr;
+  // matrix memory: gate biases, the output norm's weight (all heads), column of the gate pre-activations
+  float* t_ib = nullptr; float* t_fb = nullptr; float* t_norm = nullptr; int c_i = 0;
 };
 
 }  // namespace hy
@@ -77,6 +88,7 @@ struct hy_engine {
   std::map<std::string, HostTensor> host;
   std::vector<LayerW> lw;
   void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; void* head_t = nullptr; double* inv_freq = nullptr;
+  float* embed_norm = nullptr;
   TanhNorm final_tanh{};
   // routed feed-forward: choices and weights per (token, choice) pair, the sorted order, the tile list
   int* x_ids = nullptr; float* x_wts = nullptr; int* x_counts = nullptr; int* x_offs = nullptr; int* x_fill = nullptr;
@@ -195,21 +207,42 @@ extern "C" int hy_create(const hy_model_cfg* model, const hy_layer_cfg* layers, 
       if (c.g_heads <= 0 || c.g_dim <= 0 || c.g_vdim <= 0) return bad("gated linear recurrence sizes must be positive");
       if (((size_t)c.g_dim * c.g_vdim + 2 * c.g_dim + c.g_vdim + 40) * 4 > 200 * 1024 && (c.g_dim > 128 || c.g_vdim > 256))
         return bad("gated linear recurrence: the state of one head exceeds shared memory");
+    } else if (c.mixer == HY_MIX_WINDOW) {
+      if (c.w_heads <= 0 || c.w_kv_heads <= 0 || c.w_heads % c.w_kv_heads) return bad("window attention heads must be a multiple of kv_heads");
+      if (c.w_dim <= 0 || c.w_vdim <= 0 || c.w_dim > 32 * HY_ATT_MAXD || c.w_vdim > 32 * HY_ATT_MAXD) return bad("window attention head sizes must lie in 1..640");
+      if (c.w_window < 1 || c.w_pool < 1) return bad("window and pool must be at least 1");
+      if (c.w_rot_dims < 0 || c.w_rot_dims % 2 || c.w_rot_dims > c.w_dim) return bad("rotated dimensions must be even and at most dim");
+      if (c.w_rot_values && c.w_vdim % 2) return bad("rotated values need an even vdim");
+    } else if (c.mixer == HY_MIX_MLSTM) {
+      if (c.t_heads <= 0 || c.t_dim <= 0 || c.t_vdim <= 0) return bad("matrix memory sizes must be positive");
+      if (((size_t)c.t_dim * (c.t_vdim + 1) + 2 * c.t_dim + c.t_vdim + 40) * 4 > 200 * 1024 && (c.t_dim > 128 || c.t_vdim > 255))
+        return bad("matrix memory: the state of one head exceeds shared memory");
     } else {
       return bad("unknown mixer kind");
     }
-    const bool sandwich_mixer = c.mixer == HY_MIX_SSD || c.mixer == HY_MIX_LATENT || c.mixer == HY_MIX_GLR;
-    if (sandwich_mixer != (model->block_kind == HY_BLOCK_SANDWICH)) return bad("this mixer does not belong to the model's block layout");
-    if ((c.ff_kind == HY_FF_ROUTED) != (model->block_kind == HY_BLOCK_SANDWICH) && c.ff_kind != HY_FF_NONE)
-      return bad("this feed-forward does not belong to the model's block layout");
+    const int mixer_block = (c.mixer == HY_MIX_SSD || c.mixer == HY_MIX_LATENT || c.mixer == HY_MIX_GLR) ? HY_BLOCK_SANDWICH
+                            : (c.mixer == HY_MIX_WINDOW || c.mixer == HY_MIX_MLSTM) ? HY_BLOCK_POSTNORM : HY_BLOCK_PARALLEL;
+    if (mixer_block != model->block_kind) return bad("this mixer does not belong to the model's block layout");
+    const bool ff_fits = c.ff_kind == HY_FF_NONE || (c.ff_kind == HY_FF_RELU2 && model->block_kind == HY_BLOCK_PARALLEL) ||
+                         (c.ff_kind == HY_FF_ROUTED && model->block_kind != HY_BLOCK_PARALLEL) ||
+                         (c.ff_kind == HY_FF_GATED && model->block_kind == HY_BLOCK_POSTNORM);
+    if (!ff_fits) return bad("this feed-forward does not belong to the model's block layout");
     if (c.ff_kind == HY_FF_ROUTED) {
       if (c.x_experts <= 0 || c.x_experts > 4096 || c.x_groups <= 0 || c.x_experts % c.x_groups) return bad("experts must split into equal groups");
       if (c.x_keep < 1 || c.x_keep > c.x_groups) return bad("kept groups outside 1..groups");
       if (c.x_top < 1 || c.x_top > c.x_keep * (c.x_experts / c.x_groups)) return bad("more experts per token than the kept groups hold");
       if (c.ff <= 0) return bad("expert size must be positive");
+      if (c.x_route != HY_ROUTE_SIGMOID_GROUPS && c.x_route != HY_ROUTE_TOP_SOFTMAX) return bad("unknown router kind");
+      if (c.x_act < 0 || c.x_act > 2 || c.x_shared_ff < 0) return bad("unknown expert activation or negative shared size");
+      if (model->block_kind == HY_BLOCK_SANDWICH && (c.x_plain || c.x_shared_ff || c.x_route || c.x_act))
+        return bad("norm - sublayer - norm blocks serve gated silu experts with sigmoid scores only");
+      if (model->block_kind == HY_BLOCK_POSTNORM && !c.x_plain) return bad("output-normed blocks serve experts without a gate only");
     }
+    if (c.ff_kind == HY_FF_GATED && (c.ff <= 0 || c.ff_act < 0 || c.ff_act > 2)) return bad("gated feed-forward: size or activation");
   }
-  if ((model->block_kind == HY_BLOCK_SANDWICH) != (model->norm_kind == HY_NORM_TANH)) return bad("block layout and norm kind do not go together");
+  const int want_norm = model->block_kind == HY_BLOCK_SANDWICH ? HY_NORM_TANH : model->block_kind == HY_BLOCK_POSTNORM ? HY_NORM_RMS
+                                                                                                                       : HY_NORM_RMS_OFFSET;
+  if (model->norm_kind != want_norm) return bad("block layout and norm kind do not go together");
   if (cudaSetDevice(rt->device) != cudaSuccess) return bad("cudaSetDevice failed");
   cudaStreamCreate(&h->stream);
   cudaEventCreate(&h->ev0);
@@ -520,6 +553,157 @@ int finalize_sandwich_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
   return B.rc;
 }
 
+// Rows of a [gate rows | up rows] matrix (ff each) reordered for the tensor-core product's gated epilogue: rows
+// [32 b, 32 b + 16) = gate features [16 b, 16 b + 16), rows [32 b + 16, 32 b + 32) = the up features that go with them.
+void interleave_gate_up(const float* gu, int ff, int W, std::vector<float>& il, int* rows) {
+  const int fb = (ff + 15) / 16;
+  *rows = fb * 32;
+  il.assign((size_t)*rows * W, 0.0f);
+  for (int f = 0; f < ff; ++f) {
+    memcpy(&il[((size_t)(f / 16) * 32 + f % 16) * W], gu + (size_t)f * W, (size_t)W * 4);
+    memcpy(&il[((size_t)(f / 16) * 32 + 16 + f % 16) * W], gu + (size_t)(ff + f) * W, (size_t)W * 4);
+  }
+}
+
+void* upload_rotation(hy_engine* h, const std::vector<double>& f) {
+  void* dv = nullptr;
+  if (dev_alloc(h, &dv, f.size() * 8, &h->bytes_w) != HY_OK) return nullptr;
+  cudaMemcpy(dv, f.data(), f.size() * 8, cudaMemcpyHostToDevice);
+  return dv;
+}
+
+// One layer of a model whose sublayers read the stream itself and are RMS-normed on the way back: the two norms and layer
+// scales, the mixer's merged input projection with its small tensors, output projection, cache or state, and the
+// feed-forward (gated dense, or routed plain experts with a router bias and a shared expert).
+int finalize_postnorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
+  const hy_layer_cfg& c = h->lc[i];
+  const hy_runtime_cfg& rt = h->rt;
+  LayerW& L = h->lw[i];
+  const int W = h->m.width;
+  const std::string p = "l" + std::to_string(i) + ".", d = p + "mix.";
+  if (auto t = B.get(p + "norm1", W, -1)) L.pn1 = B.up_f32(t->v);
+  if (auto t = B.get(p + "ls1", W, -1)) L.ls1 = B.up_f32(t->v);
+  std::vector<float> win;
+  int n_in = 0, k_out = 0;
+  if (c.mixer == HY_MIX_WINDOW) {
+    const int H = c.w_heads, G = c.w_kv_heads, D = c.w_dim, Dv = c.w_vdim;
+    L.c_q = 0; L.c_k = H * D; L.c_v = H * D + G * D;
+    n_in = H * D + G * D + G * Dv;
+    stack_rows(win, B.get(d + "q", H * D, W));
+    stack_rows(win, B.get(d + "k", G * D, W));
+    stack_rows(win, B.get(d + "v", G * Dv, W));
+    if (c.w_qk_norm) {
+      if (auto t = B.get(d + "q.norm", D, -1)) L.w_qn = B.up_f32(t->v);
+      if (auto t = B.get(d + "k.norm", D, -1)) L.w_kn = B.up_f32(t->v);
+    }
+    std::vector<double> f((size_t)c.w_rot_dims / 2), fv(c.w_rot_values ? (size_t)Dv / 2 : 0);
+    for (size_t j = 0; j < f.size(); ++j) f[j] = pow((double)c.w_rot_base, -2.0 * (double)j / (double)c.w_rot_dims);
+    for (size_t j = 0; j < fv.size(); ++j) fv[j] = pow((double)c.w_rot_base, -2.0 * (double)j / (double)Dv);
+    L.rot = Rotation{(const double*)upload_rotation(h, f), (int)f.size(), 1.0f};
+    L.rot_v = Rotation{(const double*)upload_rotation(h, fv), (int)fv.size(), 1.0f};
+    k_out = H * Dv;
+    mx.in = std::max(mx.in, n_in); mx.cv = std::max(mx.cv, H * D); mx.f1 = std::max(mx.f1, Dv);
+    const size_t rows = (size_t)rt.num_pages * G * rt.page_size;
+    const size_t prow = (size_t)rt.num_pages * G * window_block_slots(rt.page_size, c.w_pool);
+    if (dev_alloc(h, &L.cache, rows * D * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+    if (dev_alloc(h, &L.cache_v, rows * Dv * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+    if (dev_alloc(h, &L.pool_k, prow * D * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+    if (dev_alloc(h, &L.pool_v, prow * Dv * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+  } else {
+    const int H = c.t_heads, nq = H * c.t_dim, nv = H * c.t_vdim;
+    L.c_q = 0; L.c_k = nq; L.c_v = 2 * nq; L.c_g = 2 * nq + nv; L.c_i = 2 * nq + 2 * nv;
+    n_in = L.c_i + 2 * H;
+    stack_rows(win, B.get(d + "q", nq, W));
+    stack_rows(win, B.get(d + "k", nq, W));
+    stack_rows(win, B.get(d + "v", nv, W));
+    stack_rows(win, B.get(d + "g", nv, W));
+    stack_rows(win, B.get(d + "i", H, W));
+    stack_rows(win, B.get(d + "f", H, W));
+    if (auto t = B.get(d + "i.b", H, -1)) L.t_ib = B.up_f32(t->v);
+    if (auto t = B.get(d + "f.b", H, -1)) L.t_fb = B.up_f32(t->v);
+    if (auto t = B.get(d + "norm", nv, -1)) L.t_norm = B.up_f32(t->v);
+    k_out = nv;
+    mx.in = std::max(mx.in, L.c_i); mx.f1 = std::max(mx.f1, 2 * H);
+    const size_t per_head = (size_t)c.t_dim * (c.t_vdim + 1) + 1;
+    if (dev_alloc(h, (void**)&L.rec_state, (size_t)rt.num_slots * H * per_head * 4, &h->bytes_state)) return HY_ERR_CUDA;
+  }
+  const HostTensor* wo = B.get(d + "o", W, k_out);
+  if (B.rc != HY_OK) return B.rc;
+  L.n_in = n_in; L.c_up = n_in;
+  L.w_in = B.up(win);
+  L.w_in_t = B.up_tiled(win, n_in, W);
+  L.k_out = k_out;
+  L.w_out = B.up(wo->v);
+  L.w_out_t = B.up_tiled(wo->v, W, k_out);
+  mx.out = std::max(mx.out, k_out);
+  mx.f2 = std::max(mx.f2, W);
+  if (c.ff_kind == HY_FF_NONE) return B.rc;
+  if (auto t = B.get(p + "norm2", W, -1)) L.pn2 = B.up_f32(t->v);
+  if (auto t = B.get(p + "ls2", W, -1)) L.ls2 = B.up_f32(t->v);
+  const int ff = c.ff;
+  if (c.ff_kind == HY_FF_GATED) {
+    std::vector<float> gu;
+    stack_rows(gu, B.get(p + "mlp.gate", ff, W));
+    stack_rows(gu, B.get(p + "mlp.up", ff, W));
+    const HostTensor* dn = B.get(p + "mlp.down", W, ff);
+    if (B.rc != HY_OK) return B.rc;
+    L.w_ff_in = B.up(gu);
+    if (h->m.dtype == HY_DTYPE_BF16 && W % 8 == 0 && ff % 8 == 0) {
+      std::vector<float> il;
+      interleave_gate_up(gu.data(), ff, W, il, &L.ff_rows);
+      L.w_ff_in_t = B.up_tiled(il, L.ff_rows, W);
+    }
+    L.w_ff_down = B.up(dn->v);
+    L.w_ff_down_t = B.up_tiled(dn->v, W, ff);
+    mx.in = std::max(mx.in, 2 * ff);
+    mx.out = std::max(mx.out, ff);
+    return B.rc;
+  }
+  const int E = c.x_experts;
+  if (auto t = B.get(p + "mlp.router", E, W)) { L.w_router = B.up(t->v); L.w_router_t = B.up_tiled(t->v, E, W); }
+  if (c.x_route == HY_ROUTE_TOP_SOFTMAX) { if (auto t = B.get(p + "mlp.router.b", E, -1)) L.x_rb = B.up_f32(t->v); }
+  std::vector<float> up, dn;
+  up.reserve((size_t)E * ff * W);
+  dn.reserve((size_t)E * W * ff);
+  for (int e = 0; e < E && B.rc == HY_OK; ++e) {
+    const std::string x = p + "mlp.e" + std::to_string(e) + ".";
+    stack_rows(up, B.get(x + "up", ff, W));
+    stack_rows(dn, B.get(x + "down", W, ff));
+  }
+  if (B.rc != HY_OK) return B.rc;
+  L.w_gu = B.up(up);
+  L.w_down = B.up(dn);
+  if (h->m.dtype == HY_DTYPE_BF16 && W % 8 == 0 && ff % 8 == 0) {
+    std::vector<uint16_t> all, one;
+    for (int e = 0; e < E; ++e) {
+      pack_tiles(&up[(size_t)e * ff * W], ff, W, one);
+      all.insert(all.end(), one.begin(), one.end());
+      L.gu_t_stride = one.size();
+    }
+    L.gu_rows = ff;
+    if (dev_alloc(h, &L.w_gu_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+    cudaMemcpy(L.w_gu_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
+    all.clear();
+    for (int e = 0; e < E; ++e) {
+      pack_tiles(&dn[(size_t)e * W * ff], W, ff, one);
+      all.insert(all.end(), one.begin(), one.end());
+      L.down_t_stride = one.size();
+    }
+    if (dev_alloc(h, &L.w_down_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+    cudaMemcpy(L.w_down_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
+  }
+  if (c.x_shared_ff > 0) {
+    const int sf = c.x_shared_ff;
+    if (auto t = B.get(p + "mlp.shared.up", sf, W)) { L.w_sh_up = B.up(t->v); L.w_sh_up_t = B.up_tiled(t->v, sf, W); }
+    if (auto t = B.get(p + "mlp.shared.down", W, sf)) { L.w_sh_down = B.up(t->v); L.w_sh_down_t = B.up_tiled(t->v, W, sf); }
+    mx.out = std::max(mx.out, sf);
+  }
+  mx.f1 = std::max(mx.f1, E);
+  mx.in = std::max(mx.in, c.x_top * ((ff + 7) & ~7));
+  mx.f2 = std::max(mx.f2, (c.x_top + 1) * W);
+  return B.rc;
+}
+
 // rows of several [n_i, k] matrices stacked
 void stack_rows(std::vector<float>& dst, const HostTensor* t) { if (t) dst.insert(dst.end(), t->v.begin(), t->v.end()); }
 
@@ -535,7 +719,11 @@ extern "C" int hy_finalize(hy_handle h) {
   if (auto t = B.get("embed", V, W)) h->embed = B.up(t->v);
   if (h->m.norm_kind == HY_NORM_TANH) tanh_norm_load(B, "final.norm", W, &h->final_tanh);
   else if (auto t = B.get("final.norm", W, -1)) h->final_norm = B.up(t->v);
-  if (auto t = B.get("head", V, W)) { h->head = B.up(t->v); h->head_t = B.up_tiled(t->v, V, W); }
+  if (h->m.embed_norm) { if (auto t = B.get("embed.norm", W, -1)) h->embed_norm = B.up_f32(t->v); }
+  if (h->m.tied_head) {
+    h->head = h->embed;
+    if (auto t = B.get("embed", V, W)) h->head_t = B.up_tiled(t->v, V, W);
+  } else if (auto t = B.get("head", V, W)) { h->head = B.up(t->v); h->head_t = B.up_tiled(t->v, V, W); }
   if (h->m.pos_kind == HY_POS_SINUSOID) {
     std::vector<double> f((W + 1) / 2);
     for (size_t i = 0; i < f.size(); ++i) f[i] = pow(10000.0, -2.0 * (double)i / (double)W);
@@ -550,8 +738,8 @@ extern "C" int hy_finalize(hy_handle h) {
   for (size_t i = 0; i < h->lc.size() && B.rc == HY_OK; ++i) {
     const hy_layer_cfg& c = h->lc[i];
     LayerW& L = h->lw[i];
-    if (h->m.block_kind == HY_BLOCK_SANDWICH) {
-      const int rc = finalize_sandwich_layer(h, B, i, mx);
+    if (h->m.block_kind != HY_BLOCK_PARALLEL) {
+      const int rc = h->m.block_kind == HY_BLOCK_SANDWICH ? finalize_sandwich_layer(h, B, i, mx) : finalize_postnorm_layer(h, B, i, mx);
       if (rc != HY_OK) return rc;
       continue;
     }
@@ -1016,9 +1204,9 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
         rows_attr = true;
       }
       expert_rows_kernel<AT, WT, AT, true><<<dim3(std::min((ff + 7) / 8, 256), P), 256, (size_t)W * sizeof(AT), s>>>(
-          hb, W, h->x_ids, top, 1, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, pin, ldh);
+          hb, W, h->x_ids, top, 1, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, pin, ldh, 0);
       expert_rows_kernel<AT, WT, float, false><<<dim3(std::min((W + 7) / 8, 256), P), 256, (size_t)ff * sizeof(AT), s>>>(
-          pin, ldh, h->x_ids, top, 0, (const WT*)L.w_down, (size_t)W * ff, W, ff, ys, W);
+          pin, ldh, h->x_ids, top, 0, (const WT*)L.w_down, (size_t)W * ff, W, ff, ys, W, -1);
     } else if (tc_experts) {
       if constexpr (std::is_same<AT, bf16>::value) {
         static bool attr_set = false;
@@ -1040,13 +1228,212 @@ int sandwich_layer(hy_engine* h, const Batch& b, size_t li) {
     } else {
       const int tiles = std::min(h->x_max_tiles, P / HY_XT + NE + 1);
       expert_gemm_simt_kernel<AT, WT, AT, true><<<dim3((ff + 63) / 64, tiles), 256, 0, s>>>(
-          hb, W, h->x_row_tok, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, pin, ldh);
+          hb, W, h->x_row_tok, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, pin, ldh, 0);
       expert_gemm_simt_kernel<AT, WT, float, false><<<dim3((W + 63) / 64, tiles), 256, 0, s>>>(
-          pin, ldh, nullptr, (const WT*)L.w_down, (size_t)W * ff, W, ff, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, ys, W);
+          pin, ldh, nullptr, (const WT*)L.w_down, (size_t)W * ff, W, ff, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, ys, W, -1);
     }
     expert_combine_kernel<AT><<<T, 256, 0, s>>>(ys, W, few ? nullptr : h->x_pair_row, h->x_wts, top, W, L.n2b, L.ls2, h->x, after_ff, hb);
     h->launches += 3;
   }
+  return HY_OK;
+}
+
+// x <- x + ls * rms(y) * w for a sublayer's output y [T, ldy] (or the mixture of expert rows), and hb <- x in the
+// activation type for the next sublayer.
+template <typename AT>
+void post_norm_add(hy_engine* h, int T, const float* y, int ldy, const float* rows, const int* pair_row, const float* wts, int top,
+                   const float* shared_rows, const float* w, const float* ls, int add) {
+  const int W = h->m.width;
+  static bool attr = false;                                  // per AT: this function is a template
+  if (!attr) { cudaFuncSetAttribute(post_norm_add_kernel<AT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  post_norm_add_kernel<AT><<<T, 256, (size_t)W * 4, h->stream>>>(y, ldy, rows, W, pair_row, wts, top, shared_rows, w, ls, h->m.norm_eps,
+                                                               W, add, h->x, (AT*)h->hbuf);
+  h->launches++;
+}
+
+// One layer of a model whose sublayers read the stream itself:  x += ls1 * rms(mixer(x)) * w1;  x += ls2 * rms(ff(x)) * w2.
+// The norm needs the whole row's mean square, so it cannot ride in the epilogue of the product that makes the row's
+// tiles: the output projections leave fp32 rows, and one kernel per sublayer norms, scales, adds and writes the updated
+// stream in both types.
+template <typename AT>
+int postnorm_layer(hy_engine* h, const Batch& b, size_t li) {
+  typedef AT WT;
+  const hy_layer_cfg& c = h->lc[li];
+  const LayerW& L = h->lw[li];
+  const int W = h->m.width, T = b.T, E = b.E;
+  const float eps = h->m.norm_eps;
+  cudaStream_t s = h->stream;
+  AT* hb = (AT*)h->hbuf; AT* pin = (AT*)h->pin; AT* cat = (AT*)h->cat; AT* cv = (AT*)h->cv;
+  if (c.mixer == HY_MIX_WINDOW) {
+    const WindowCfg wc{c.w_heads, c.w_kv_heads, c.w_dim, c.w_vdim, c.w_window, c.w_pool, c.w_rot_dims, c.w_rot_values, c.w_qk_norm, c.w_scale};
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, to_buf(pin, h->ld_pin), L.w_in_t);
+    }
+    {
+      ProfScope ps(h, HY_PROF_CONV);
+      window_prep_kernel<AT><<<T, 128, (size_t)(2 * L.rot.pairs + 2 * L.rot_v.pairs + 2) * 4, s>>>(
+          b, pin, h->ld_pin, L.c_q, L.c_k, L.c_v, wc, L.w_qn, L.w_kn, eps, L.rot, L.rot_v, cv, h->ld_cv, (AT*)L.cache, (AT*)L.cache_v,
+          h->f1, h->ld_f1);
+      int most = 0;                                           // blocks one entry completes in this step
+      for (int e = 0; e < E; ++e) {
+        const int p0 = h->step_pos0[e], end = p0 + h->step_start[e + 1] - h->step_start[e];
+        most = std::max(most, end / c.w_pool - p0 / c.w_pool);
+      }
+      h->launches++;
+      if (most > 0) {
+        window_pool_kernel<AT><<<dim3(most, E), 128, 0, s>>>(b, wc, (const AT*)L.cache, (const AT*)L.cache_v, (AT*)L.pool_k, (AT*)L.pool_v);
+        h->launches++;
+      }
+    }
+    {
+      ProfScope ps(h, HY_PROF_ATTN);
+      window_attn_kernel<AT, AT><<<(T * c.w_heads + 3) / 4, 128, 4 * c.w_dim * sizeof(float), s>>>(
+          b, cv, h->ld_cv, wc, (const AT*)L.cache, (const AT*)L.cache_v, (const AT*)L.pool_k, (const AT*)L.pool_v, h->f1, h->ld_f1, cat,
+          h->ld_cat);
+      h->launches++;
+    }
+  } else {
+    const int H = c.t_heads, dk = c.t_dim, dv = c.t_vdim;
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      GemmOut o{pin, h->ld_pin, L.c_i, h->f1, h->ld_f1, 0, nullptr, 0, 1.0f};
+      o.out2_f32 = 1;                                         // the gates' pre-activations stay fp32
+      gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, o, L.w_in_t);
+    }
+    ProfScope ps(h, HY_PROF_DELTA);
+    static bool attr = false;
+    if (!attr) {
+      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(mlstm_kernel<AT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      attr = true;
+    }
+#define HY_MLSTM_ARGS b, pin, h->ld_pin, L.c_q, L.c_k, L.c_v, L.c_g, h->f1, h->ld_f1, 0, H, L.t_ib, L.t_fb, L.t_norm, H, dk, dv, \
+    c.t_gate_cap, eps, L.rec_state, cat, h->ld_cat
+    const int nthr = ((dv + 1 + 31) / 32) * 32;               // one thread per value column and one for the normaliser
+    auto msm = [](int dr, int nt) { return (size_t)(HY_MLSTM_TB * (2 * dr + 2 * nt) + 5 * HY_MLSTM_TB + 4) * 4; };
+    if (dk <= 32 && nthr <= 512) mlstm_reg_kernel<AT, 32><<<dim3(H, E), nthr, msm(32, nthr), s>>>(HY_MLSTM_ARGS);
+    else if (dk <= 64 && nthr <= 512) mlstm_reg_kernel<AT, 64><<<dim3(H, E), nthr, msm(64, nthr), s>>>(HY_MLSTM_ARGS);
+    else if (dk <= 128 && nthr <= 256) mlstm_reg_kernel<AT, 128><<<dim3(H, E), nthr, msm(128, nthr), s>>>(HY_MLSTM_ARGS);
+    else mlstm_kernel<AT><<<dim3(H, E), 256, ((size_t)dk * (dv + 1) + 2 * dk + dv + 1 + 40) * 4, s>>>(HY_MLSTM_ARGS);
+#undef HY_MLSTM_ARGS
+    h->launches++;
+  }
+  {
+    ProfScope ps(h, HY_PROF_GEMM_OUT);
+    gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, to_buf(h->f2, h->ld_f2), L.w_out_t);
+  }
+  {
+    ProfScope ps(h, HY_PROF_NORM);
+    post_norm_add<AT>(h, T, h->f2, h->ld_f2, nullptr, nullptr, nullptr, 0, nullptr, L.pn1, L.ls1, 1);
+  }
+  if (c.ff_kind == HY_FF_NONE) return HY_OK;
+  if (c.ff_kind == HY_FF_GATED) {
+    const int ff = c.ff;
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      bool fused = false;
+      if constexpr (std::is_same<AT, bf16>::value) {
+        // more rows than the few-row kernel takes: the tensor-core product over gate / up rows that alternate in blocks of
+        // 16, the gated activation in its epilogue
+        if (T > 8 && L.w_ff_in_t && W % 8 == 0) {
+          GemmOut o{cat, h->ld_cat, ff, nullptr, 0, 2, nullptr, 0, 1.0f};
+          o.act_kind = c.ff_act;
+          gemm<AT, WT, AT>(h, hb, W, (const WT*)nullptr, W, T, L.ff_rows, W, o, L.w_ff_in_t);
+          fused = true;
+        }
+      }
+      if (!fused) {
+        gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_ff_in, W, T, 2 * ff, W, to_buf(pin, h->ld_pin));
+        gated_act_kernel<AT><<<dim3((ff + 255) / 256, T), 256, 0, s>>>(pin, h->ld_pin, ff, c.ff_act, cat, h->ld_cat);
+        h->launches++;
+      }
+    }
+    {
+      ProfScope ps(h, HY_PROF_GEMM_OUT);
+      gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_ff_down, ff, T, W, ff, to_buf(h->f2, h->ld_f2), L.w_ff_down_t);
+    }
+    ProfScope ps(h, HY_PROF_NORM);
+    post_norm_add<AT>(h, T, h->f2, h->ld_f2, nullptr, nullptr, nullptr, 0, nullptr, L.pn2, L.ls2, 1);
+    return HY_OK;
+  }
+  // routed plain experts: down(act(up x)), beside a shared expert of the same form
+  const int NE = c.x_experts, top = c.x_top, ff = c.ff, P = T * top, ldh = (ff + 7) & ~7;
+  const bool tc_experts = std::is_same<AT, bf16>::value && L.w_gu_t != nullptr;
+  static const int rows_max_env = getenv("HY_EXPERT_ROWS_MAX") ? atoi(getenv("HY_EXPERT_ROWS_MAX")) : -1;   // developer switch
+  const bool few = P <= (rows_max_env >= 0 ? rows_max_env : tc_experts ? 8 : 16);
+  {
+    ProfScope ps(h, HY_PROF_ROUTE);
+    gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_router, W, T, NE, W, to_buf(h->f1, h->ld_f1), L.w_router_t);
+    if (c.x_route == HY_ROUTE_TOP_SOFTMAX) {
+      route_top_kernel<<<T, 32, (size_t)NE * 4, s>>>(h->f1, h->ld_f1, L.x_rb, NE, top, h->x_ids, h->x_wts, few ? nullptr : h->x_counts);
+    } else {
+      const RouteCfg rc{NE, top, c.x_groups, c.x_keep, c.x_scale};
+      route_kernel<<<T, 32, (size_t)(NE + c.x_groups) * 4, s>>>(h->f1, h->ld_f1, rc, h->x_ids, h->x_wts, few ? nullptr : h->x_counts);
+    }
+    h->launches++;
+    if (!few) {
+      route_offsets_kernel<<<1, 32, 0, s>>>(h->x_counts, NE, tc_experts ? 128 : HY_XT, h->x_offs, h->x_fill, h->x_tile_e,
+                                            h->x_tile_r0, h->x_meta);
+      route_scatter_kernel<<<(P + 255) / 256, 256, 0, s>>>(P, top, h->x_ids, h->x_offs, h->x_fill, h->x_row_tok, h->x_pair_row);
+      h->launches += 2;
+    }
+  }
+  float* ys = h->f2;                                          // [pairs (+ tokens: the shared expert's rows), width] fp32
+  float* shared_rows = nullptr;
+  {
+    ProfScope ps(h, HY_PROF_EXPERTS);
+    if (few) {
+      static bool rows_attr = false;
+      if (!rows_attr) {
+        cudaFuncSetAttribute(expert_rows_kernel<AT, WT, AT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(expert_rows_kernel<AT, WT, float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        rows_attr = true;
+      }
+      expert_rows_kernel<AT, WT, AT, false><<<dim3(std::min((ff + 7) / 8, 256), P), 256, (size_t)W * sizeof(AT), s>>>(
+          hb, W, h->x_ids, top, 1, (const WT*)L.w_gu, (size_t)ff * W, ff, W, pin, ldh, c.x_act);
+      expert_rows_kernel<AT, WT, float, false><<<dim3(std::min((W + 7) / 8, 256), P), 256, (size_t)ff * sizeof(AT), s>>>(
+          pin, ldh, h->x_ids, top, 0, (const WT*)L.w_down, (size_t)W * ff, W, ff, ys, W, -1);
+    } else if (tc_experts) {
+      if constexpr (std::is_same<AT, bf16>::value) {
+        static bool attr_set = false;
+        if (!attr_set) {
+          cudaFuncSetAttribute(gemm_tc_kernel<bf16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
+          cudaFuncSetAttribute(gemm_tc_kernel<float, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
+          attr_set = true;
+        }
+        const int tiles = std::min(h->x_max_tiles, P / 128 + NE + 1);
+        const TcGroup g1{h->x_meta, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_row_tok, L.gu_t_stride};
+        const TcGroup g2{h->x_meta, h->x_offs, h->x_tile_e, h->x_tile_r0, nullptr, L.down_t_stride};
+        GemmOut o1 = to_buf(pin, ldh);
+        o1.act2 = 3; o1.act_kind = c.x_act;
+        gemm_tc_kernel<bf16, 128><<<dim3((ff + 127) / 128, tiles), 192, tc_smem_bytes(128), s>>>(
+            hb, W, (const bf16*)L.w_gu_t, P, ff, W, o1, h->err_d, g1);
+        GemmOut o2 = to_buf(ys, W);
+        gemm_tc_kernel<float, 128><<<dim3((W + 127) / 128, tiles), 192, tc_smem_bytes(128), s>>>(
+            pin, ldh, (const bf16*)L.w_down_t, P, W, ff, o2, h->err_d, g2);
+      }
+    } else {
+      const int tiles = std::min(h->x_max_tiles, P / HY_XT + NE + 1);
+      expert_gemm_simt_kernel<AT, WT, AT, false><<<dim3((ff + 63) / 64, tiles), 256, 0, s>>>(
+          hb, W, h->x_row_tok, (const WT*)L.w_gu, (size_t)ff * W, ff, W, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, pin, ldh, c.x_act);
+      expert_gemm_simt_kernel<AT, WT, float, false><<<dim3((W + 63) / 64, tiles), 256, 0, s>>>(
+          pin, ldh, nullptr, (const WT*)L.w_down, (size_t)W * ff, W, ff, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, ys, W, -1);
+    }
+    h->launches += 2;
+    if (c.x_shared_ff > 0) {
+      const int sf = c.x_shared_ff;
+      shared_rows = ys + (size_t)P * W;
+      GemmOut o = to_buf(cat, h->ld_cat);
+      o.act2 = 3; o.act_kind = c.x_act;
+      gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_sh_up, W, T, sf, W, o, L.w_sh_up_t);
+      gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_sh_down, sf, T, W, sf, to_buf(shared_rows, W), L.w_sh_down_t);
+    }
+  }
+  ProfScope ps(h, HY_PROF_NORM);
+  post_norm_add<AT>(h, T, nullptr, 0, ys, few ? nullptr : h->x_pair_row, h->x_wts, top, shared_rows, L.pn2, L.ls2, 1);
   return HY_OK;
 }
 
@@ -1061,19 +1448,22 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
     ProfScope ps(h, HY_PROF_NORM);
     embed_kernel<WT><<<T, 128, 0, s>>>(b, (const WT*)h->embed, h->inv_freq, h->m.emb_scale, W, h->x);
     h->launches++;
+    // output-normed blocks read the stream itself: it leaves here in the activation type too, normed when the model says so
+    if (h->m.block_kind == HY_BLOCK_POSTNORM) post_norm_add<AT>(h, T, h->x, W, nullptr, nullptr, nullptr, 0, nullptr, h->embed_norm, nullptr, 0);
   }
   for (size_t li = 0; li < h->lc.size(); ++li) {
     const hy_layer_cfg& c = h->lc[li];
     const LayerW& L = h->lw[li];
-    if (h->m.block_kind == HY_BLOCK_SANDWICH) {
-      sandwich_layer<AT>(h, b, li);
+    if (h->m.block_kind != HY_BLOCK_PARALLEL) {
+      if (h->m.block_kind == HY_BLOCK_SANDWICH) sandwich_layer<AT>(h, b, li);
+      else postnorm_layer<AT>(h, b, li);
       if (layers_out) cudaMemcpyAsync(layers_out + li * (size_t)T * W, h->x, (size_t)T * W * 4, cudaMemcpyDeviceToHost, s);
       continue;
     }
     const int ff = c.ff_kind == HY_FF_NONE ? 0 : c.ff;
     {
       ProfScope ps(h, HY_PROF_NORM);
-      rmsnorm_kernel<WT, AT><<<T, 256, 0, s>>>(h->x, nullptr, (const WT*)L.norm1, eps, W, hb);
+      rmsnorm_kernel<WT, AT><<<T, 256, 0, s>>>(h->x, nullptr, (const WT*)L.norm1, eps, W, 1.0f, hb);
       h->launches++;
     }
     // every projection that reads the normed input, in one product; the feed-forward's hidden part leaves activated,
@@ -1206,7 +1596,8 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
   if (n_want > 0) {
     ProfScope ps(h, HY_PROF_HEAD);
     if (h->m.norm_kind == HY_NORM_TANH) tanh_norm_kernel<AT><<<n_want, 256, 0, s>>>(h->x, want_d, h->final_tanh, W, (AT*)h->hw);
-    else rmsnorm_kernel<WT, AT><<<n_want, 256, 0, s>>>(h->x, want_d, (const WT*)h->final_norm, eps, W, (AT*)h->hw);
+    else rmsnorm_kernel<WT, AT><<<n_want, 256, 0, s>>>(h->x, want_d, (const WT*)h->final_norm, eps, W,
+                                                       h->m.norm_kind == HY_NORM_RMS ? 0.0f : 1.0f, (AT*)h->hw);
     h->launches++;
     GemmOut o = to_buf(h->logits, h->m.vocab);
     o.alpha = h->m.logit_scale;

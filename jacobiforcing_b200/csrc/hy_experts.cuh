@@ -61,6 +61,41 @@ __global__ void __launch_bounds__(32) route_kernel(const float* __restrict__ log
   for (int k = 0; k < c.top; ++k) wts[(size_t)t * c.top + k] *= f;
 }
 
+// The other way to score: the `top` largest router logits (bias added here, ties to the lower index), weights = softmax
+// over the chosen logits alone.  One warp per token, lane 0 makes the choice.
+__global__ void __launch_bounds__(32) route_top_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ bias,
+                                                       int experts, int top, int* __restrict__ ids, float* __restrict__ wts,
+                                                       int* __restrict__ counts) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  float* s = reinterpret_cast<float*>(hy_smem);                // [experts] logits, -inf once chosen
+  const int t = blockIdx.x, lane = threadIdx.x;
+  for (int e = lane; e < experts; e += 32) s[e] = logits[(size_t)t * ldl + e] + (bias ? bias[e] : 0.0f);
+  __syncwarp();
+  if (lane != 0) return;
+  float mx = 0.0f, sum = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    int best = 0; float bv = -INFINITY;
+    for (int e = 0; e < experts; ++e) if (s[e] > bv) { bv = s[e]; best = e; }
+    if (k == 0) mx = bv;                                       // the first choice is the largest: the softmax's maximum
+    const float w = expf(bv - mx);
+    ids[(size_t)t * top + k] = best;
+    wts[(size_t)t * top + k] = w;
+    sum += w;
+    s[best] = -INFINITY;
+    if (counts) atomicAdd(&counts[best], 1);
+  }
+  const float f = 1.0f / sum;
+  for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= f;
+}
+
+// out[t, f] = act(in[t, f]) * in[t, n + f]: the gated pair of a dense feed-forward whose gate and up rows are stacked.
+template <typename AT>
+__global__ void gated_act_kernel(const AT* __restrict__ in, int ldi, int n, int act, AT* __restrict__ out, int ldo) {
+  const int t = blockIdx.y;
+  const int f = blockIdx.x * blockDim.x + threadIdx.x;
+  if (f < n) out[(size_t)t * ldo + f] = from_f<AT>(act_f(act, to_f(in[(size_t)t * ldi + f])) * to_f(in[(size_t)t * ldi + n + f]));
+}
+
 // Tiles of tile_rows rows of one expert (HY_XT for the SIMT product, 128 for the tensor-core product).  meta: [0] number
 // of tiles; offs [experts + 1]; fill [experts] zeroed here.
 constexpr int HY_XT = 64;
@@ -93,14 +128,15 @@ __global__ void route_scatter_kernel(int pairs, int top, const int* __restrict__
 }
 
 // Grouped product over the sorted rows: C[row, n] = sum_k A[src(row), k] W_e[n, k], e the expert of the row's tile.
-// GLU: W_e is [2 N, K] (gate rows, then up rows) and the result is silu(gate) * up.  src(row) = row_map[row] when a map
+// GLU: W_e is [2 N, K] (gate rows, then up rows) and the result is act(gate) * up; without GLU the result passes through
+// the activation when act >= 0 (act: 0 silu, 1 tanh-gelu, 2 erf-gelu; see act_f).  src(row) = row_map[row] when a map
 // is given (activation rows of the tokens), else row.  Tiled SIMT, fp32 FMAs in k order: both builds can use it.
 template <typename TA, typename TW, typename TO, bool GLU>
 __global__ void __launch_bounds__(256) expert_gemm_simt_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ row_map,
                                                                const TW* __restrict__ W, size_t w_stride, int N, int K,
                                                                const int* __restrict__ offs, const int* __restrict__ tile_expert,
                                                                const int* __restrict__ tile_row0, const int* __restrict__ meta,
-                                                               TO* __restrict__ out, int ldo) {
+                                                               TO* __restrict__ out, int ldo, int act) {
   constexpr int BM = HY_XT, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[GLU ? 2 : 1][BK][BN + 4];
@@ -153,7 +189,7 @@ __global__ void __launch_bounds__(256) expert_gemm_simt_kernel(const TA* __restr
       for (int j = 0; j < 4; ++j) {
         const int n = n0 + tx * 4 + j;
         if (n >= N) continue;
-        const float c = GLU ? silu_f(acc[i][j]) * acc2[GLU ? i : 0][j] : acc[i][j];
+        const float c = GLU ? act_f(act, acc[i][j]) * acc2[GLU ? i : 0][j] : act >= 0 ? act_f(act, acc[i][j]) : acc[i][j];
         out[(size_t)(r0 + r) * ldo + n] = from_f<TO>(c);
       }
     }
@@ -166,7 +202,7 @@ __global__ void __launch_bounds__(256) expert_gemm_simt_kernel(const TA* __restr
 template <typename TA, typename TW, typename TO, bool GLU>
 __global__ void __launch_bounds__(256) expert_rows_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ ids, int top,
                                                           int a_per_token, const TW* __restrict__ W, size_t w_stride, int N, int K,
-                                                          TO* __restrict__ out, int ldo) {
+                                                          TO* __restrict__ out, int ldo, int act) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
   TA* As = reinterpret_cast<TA*>(hy_smem);
   constexpr int VEC = 16 / sizeof(TW);
@@ -203,7 +239,7 @@ __global__ void __launch_bounds__(256) expert_rows_kernel(const TA* __restrict__
     }
     acc = warp_sum(acc);
     if (GLU) acc2 = warp_sum(acc2);
-    if (lane == 0) out[(size_t)pair * ldo + n] = from_f<TO>(GLU ? silu_f(acc) * acc2 : acc);
+    if (lane == 0) out[(size_t)pair * ldo + n] = from_f<TO>(GLU ? act_f(act, acc) * acc2 : act >= 0 ? act_f(act, acc) : acc);
   }
 }
 

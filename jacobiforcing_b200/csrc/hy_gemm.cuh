@@ -44,7 +44,8 @@ struct TcGroup {
 };
 
 // GemmOut.act2 == 2 (gated pair): the weight rows alternate 16 gate features and the 16 up features that go with them, so
-// lanes l and l + 16 of an epilogue warp hold one pair; silu(gate) * up leaves through out1 at feature n / 2.
+// lanes l and l + 16 of an epilogue warp hold one pair; act(gate) * up (act = GemmOut.act_kind) leaves through out1 at
+// feature n / 2.
 template <typename TO, int BT>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X, int lda, const bf16* __restrict__ Wt, int T,
                                                       int N, int K, GemmOut o, int* err, TcGroup grp) {
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X
             const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
             const int f = ((n0 + warp * 32) >> 1) + lane;
             if (lane < 16 && f < o.split && t0 + c0 + j < T)
-              ((TO*)o.out1)[(size_t)(t0 + c0 + j) * o.ld1 + f] = from_f<TO>(silu_f(mine) * other);
+              ((TO*)o.out1)[(size_t)(t0 + c0 + j) * o.ld1 + f] = from_f<TO>(act_f(o.act_kind, mine) * other);
           }
           continue;
         }

@@ -25,6 +25,10 @@ template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __flo
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float silu_f(float z) { return z * sigmoid_f(z); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
+// activation by kind: 0 silu, 1 the tanh form of gelu, 2 gelu with the error function
+__device__ __forceinline__ float act_f(int kind, float z) { return kind == 1 ? gelu_tanh_f(z) : kind == 2 ? gelu_erf_f(z) : silu_f(z); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -96,11 +100,11 @@ __global__ void tanh_norm_kernel(const float* __restrict__ x, const int* __restr
     out[(size_t)r * width + c] = from_f<OT>(fmaf(tanhf(n.alpha * xr[c]), n.w[c], n.b[c]));
 }
 
-// ---- RMS norm with a weight stored as an offset from one (plain = 0: multiply by w itself) ------------------------------
+// ---- RMS norm; the weight is w_offset + w (1: stored as an offset from one, 0: plain) -----------------------------------------
 // rows: NULL = row r of x, else x row rows[r].  out row r.
 template <typename WT, typename OT>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const WT* __restrict__ w,
-                               float eps, int width, OT* __restrict__ out) {
+                               float eps, int width, float w_offset, OT* __restrict__ out) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
@@ -109,7 +113,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)width + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x)
-    out[(size_t)r * width + c] = from_f<OT>(xr[c] * inv * (1.0f + to_f(w[c])));
+    out[(size_t)r * width + c] = from_f<OT>(xr[c] * inv * (w_offset + to_f(w[c])));
 }
 
 // ---- generic matrix product C[t, n] = sum_k A[t, k] W[n, k], fp32 accumulation in k order -----------------------------------
@@ -120,11 +124,14 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // pass) and its layer scale, applied to the fp32 accumulator.
 // With next_w set as well, the element of the updated residual also leaves through the NEXT sublayer's input norm
 // (tanh(next_alpha x) next_w[n] + next_b[n]) into next_out [T, ldr] in the activation type: no separate norm launch.
+// act2 == 3: every column passes through the activation act_kind (act_f) before it is stored.  out2_f32: the columns from
+// `split` on leave as fp32 whatever the output type (gate pre-activations of a recurrence beside its bf16 operands).
 struct GemmOut {
   void* out1; int ld1; int split; void* out2; int ld2; int act2;
   float* resid; int ldr; float alpha;
   const float* post_w; const float* post_b; const float* post_ls; float post_alpha;
   const float* next_w; const float* next_b; float next_alpha; void* next_out; int next_f32;
+  int act_kind; int out2_f32;
 };
 
 template <typename TO>
@@ -141,9 +148,52 @@ __device__ __forceinline__ void gemm_store(const GemmOut& o, int t, int n, float
     }
     return;
   }
+  if (o.act2 == 3) c = act_f(o.act_kind, c);
   if (n < o.split) { ((TO*)o.out1)[(size_t)t * o.ld1 + n] = from_f<TO>(c); return; }
-  if (o.act2) { c = fmaxf(c, 0.0f); c = c * c; }
-  ((TO*)o.out2)[(size_t)t * o.ld2 + (n - o.split)] = from_f<TO>(c);
+  if (o.act2 == 1) { c = fmaxf(c, 0.0f); c = c * c; }
+  if (o.out2_f32) ((float*)o.out2)[(size_t)t * o.ld2 + (n - o.split)] = c;
+  else ((TO*)o.out2)[(size_t)t * o.ld2 + (n - o.split)] = from_f<TO>(c);
+}
+
+// ---- RMS norm on a sublayer's output, layer scale and the residual sum --------------------------------------------------------
+// x[t] <- (add ? x[t] : 0) + ls * y[t] / sqrt(mean(y[t]^2) + eps) * w   (ls == NULL: one), and the updated row also leaves
+// in the activation type (the next sublayer reads the stream itself).  y[t] is row t of ybuf, or, when `rows` is given,
+// the mixture of a routed feed-forward: sum_k wts[t, k] rows[pair_row ? pair_row[t top + k] : t top + k] in the order of
+// the token's choices, plus shared_rows[t] (an expert every token uses) when given.  ybuf may be x itself (add = 0).
+template <typename AT>
+__global__ void post_norm_add_kernel(const float* ybuf, int ldy, const float* __restrict__ rows, int ldr,
+                                     const int* __restrict__ pair_row, const float* __restrict__ wts, int top,
+                                     const float* __restrict__ shared_rows, const float* __restrict__ w,
+                                     const float* __restrict__ ls, float eps, int width, int add, float* x,
+                                     AT* __restrict__ next_out) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  float* ys = reinterpret_cast<float*>(hy_smem);               // [width]
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float y;
+    if (rows) {
+      y = 0.0f;
+      for (int k = 0; k < top; ++k) {
+        const int i = t * top + k;
+        y = fmaf(wts[i], rows[(size_t)(pair_row ? pair_row[i] : i) * ldr + c], y);
+      }
+      if (shared_rows) y += shared_rows[(size_t)t * ldr + c];
+    } else {
+      y = ybuf[(size_t)t * ldy + c];
+    }
+    ys[c] = y;
+    ss = fmaf(y, y, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = w ? 1.0f / sqrtf(ss / (float)width + eps) : 1.0f;      // w == NULL: no norm, the row passes as it is
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float n = ys[c] * inv * (w ? w[c] : 1.0f) * (ls ? ls[c] : 1.0f);
+    const float v = add ? x[(size_t)t * width + c] + n : n;
+    x[(size_t)t * width + c] = v;
+    if (next_out) next_out[(size_t)t * width + c] = from_f<AT>(v);
+  }
 }
 
 // Tiled SIMT kernel: any shape, any leading dimensions; the all-fp32 build's matrix product (true fp32 FMAs).

@@ -505,4 +505,177 @@ glr_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_f, int
   for (int i = tid; i < dim * vdim; i += blockDim.x) st[i] = S[i];
 }
 
+// ---- matrix memory with exponential gates under a running maximum ----------------------------------------------------------------
+// Per head, S [dim, vdim], n [dim], m (all zero at the start of a sequence, m too):
+//   li = cap tanh((i_raw + i_bias) / cap) ; lf = logsigmoid(cap tanh((f_raw + f_bias) / cap))        (cap <= 0: no cap)
+//   m' = max(lf + m, li) ; a = exp(lf + m - m') ; c = exp(li - m')
+//   S <- a S + c k v^T ; n <- a n + c k ; o = S^T q / (max(|n . q|, exp(-m')) + 1e-6) ,  q = q_raw dim^(-1/2)
+//   out = o / rms(o) * norm_w[head] * sigmoid(g)        (norm over the head's vdim)
+// The normaliser n is carried as one more value column whose value is always one: column vdim of the state, so n . q is
+// that column's read-out.  in [T, ld]: q, k at col_q, col_k (heads * dim each), v, g at col_v, col_g (heads * vdim);
+// gates [T, ldg] fp32: i_raw at col_i + head, f_raw at col_f + head.  state [slot][H][dim * (vdim + 1) + 1], m last.
+// Thread j keeps column j of the state in registers (key size <= DR); inputs of HY_MLSTM_TB tokens are staged by the
+// block, one thread walks the batch's gate recurrence (a scalar chain), one warp per token makes the output norm.
+constexpr int HY_MLSTM_TB = 16;
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float cap_f(float z, float cap) { return cap > 0.0f ? cap * tanhf(z / cap) : z; }
+
+template <typename AT, int DR>
+__global__ void __launch_bounds__(DR > 64 ? 256 : 512)
+mlstm_reg_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_k, int col_v, int col_g,
+                 const float* __restrict__ gates, int ldg, int col_i, int col_f, const float* __restrict__ i_bias,
+                 const float* __restrict__ f_bias, const float* __restrict__ norm_w, int H, int dim, int vdim, float cap,
+                 float eps, float* __restrict__ state, AT* __restrict__ out, int ldo) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  constexpr int TB = HY_MLSTM_TB;
+  const int nt = blockDim.x, nwarps = nt >> 5;
+  float* sq = reinterpret_cast<float*>(hy_smem);               // [TB][DR] scaled queries
+  float* sk = sq + TB * DR;                                    // [TB][DR] keys
+  float* sv = sk + TB * DR;                                    // [TB][nt] values, a one in column vdim
+  float* so = sv + TB * nt;                                    // [TB][nt] read-outs
+  float* sg = so + TB * nt;                                    // [5][TB]: li, lf, a, c, exp(-m); then m itself
+  const int h = blockIdx.x, e = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
+  const int vs = vdim + 1;
+  float* st = state + ((size_t)b.ent_slot[e] * H + h) * ((size_t)dim * vs + 1);
+  const bool col = tid < vs;
+  float S[DR];
+#pragma unroll
+  for (int i = 0; i < DR; ++i) S[i] = (col && i < dim && pos0 > 0) ? st[(size_t)i * vs + tid] : 0.0f;
+  if (tid == 0) sg[5 * TB] = pos0 > 0 ? st[(size_t)dim * vs] : 0.0f;
+  const float qscale = 1.0f / sqrtf((float)dim);
+  for (int j0 = 0; j0 < cnt; j0 += TB) {
+    const int nb = min(TB, cnt - j0);
+    __syncthreads();
+    for (int i = tid; i < nb * DR; i += nt) {
+      const int tt = i / DR, k = i % DR;
+      const size_t t = (size_t)(start + j0 + tt);
+      const bool ok = k < dim;
+      sq[i] = ok ? to_f(in[t * ld + col_q + h * dim + k]) * qscale : 0.0f;
+      sk[i] = ok ? to_f(in[t * ld + col_k + h * dim + k]) : 0.0f;
+    }
+    for (int i = tid; i < nb * nt; i += nt) {
+      const int tt = i / nt, k = i % nt;
+      sv[i] = k < vdim ? to_f(in[(size_t)(start + j0 + tt) * ld + col_v + h * vdim + k]) : k == vdim ? 1.0f : 0.0f;
+    }
+    if (tid < nb) {
+      const size_t t = (size_t)(start + j0 + tid);
+      sg[tid] = cap_f(gates[t * ldg + col_i + h] + i_bias[h], cap);
+      sg[TB + tid] = log_sigmoid_f(cap_f(gates[t * ldg + col_f + h] + f_bias[h], cap));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float m = sg[5 * TB];
+      for (int tt = 0; tt < nb; ++tt) {
+        const float li = sg[tt], lf = sg[TB + tt];
+        const float mn = fmaxf(lf + m, li);
+        sg[2 * TB + tt] = expf(lf + m - mn);
+        sg[3 * TB + tt] = expf(li - mn);
+        sg[4 * TB + tt] = expf(-mn);
+        m = mn;
+      }
+      sg[5 * TB] = m;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nb; ++tt) {
+      const float* ks = sk + tt * DR;
+      const float* qs = sq + tt * DR;
+      const float a = sg[2 * TB + tt];
+      const float cv = sg[3 * TB + tt] * sv[tt * nt + tid];
+      float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < DR; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[i]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[i]);
+        S[i] = fmaf(a, S[i], cv * k4.x); S[i + 1] = fmaf(a, S[i + 1], cv * k4.y);
+        S[i + 2] = fmaf(a, S[i + 2], cv * k4.z); S[i + 3] = fmaf(a, S[i + 3], cv * k4.w);
+        p0 = fmaf(S[i], q4.x, p0); p1 = fmaf(S[i + 1], q4.y, p1);
+        p2 = fmaf(S[i + 2], q4.z, p2); p3 = fmaf(S[i + 3], q4.w, p3);
+      }
+      so[tt * nt + tid] = (p0 + p1) + (p2 + p3);
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nb; tt += nwarps) {
+      const float den = 1.0f / (fmaxf(fabsf(so[tt * nt + vdim]), sg[4 * TB + tt]) + 1e-6f);
+      float o2 = 0.0f;
+      for (int k = lane; k < vdim; k += 32) { const float o = so[tt * nt + k] * den; o2 = fmaf(o, o, o2); }
+      o2 = warp_sum(o2);
+      const float inv = den / sqrtf(o2 / (float)vdim + eps);
+      const size_t t = (size_t)(start + j0 + tt);
+      for (int k = lane; k < vdim; k += 32) {
+        const float gt = sigmoid_f(to_f(in[t * ld + col_g + h * vdim + k]));
+        out[t * ldo + h * vdim + k] = from_f<AT>(so[tt * nt + k] * inv * norm_w[h * vdim + k] * gt);
+      }
+    }
+  }
+  if (col) {
+#pragma unroll
+    for (int i = 0; i < DR; ++i)
+      if (i < dim) st[(size_t)i * vs + tid] = S[i];
+  }
+  __syncthreads();
+  if (tid == 0) st[(size_t)dim * vs] = sg[5 * TB];
+}
+
+// The same recurrence for any head size whose state fits shared memory: S [dim][vdim + 1] in shared memory, a thread walks
+// the columns j = tid, tid + blockDim, ...; one token at a time.
+template <typename AT>
+__global__ void __launch_bounds__(256)
+mlstm_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_k, int col_v, int col_g,
+             const float* __restrict__ gates, int ldg, int col_i, int col_f, const float* __restrict__ i_bias,
+             const float* __restrict__ f_bias, const float* __restrict__ norm_w, int H, int dim, int vdim, float cap, float eps,
+             float* __restrict__ state, AT* __restrict__ out, int ldo) {
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  const int vs = vdim + 1;
+  float* S = reinterpret_cast<float*>(hy_smem);                // [dim][vs]
+  float* qs = S + (size_t)dim * vs;                            // [dim]
+  float* ks = qs + dim;                                        // [dim]
+  float* os = ks + dim;                                        // [vs]
+  float* red = os + vs;                                        // 33
+  const int h = blockIdx.x, e = blockIdx.y, tid = threadIdx.x;
+  const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
+  float* st = state + ((size_t)b.ent_slot[e] * H + h) * ((size_t)dim * vs + 1);
+  for (int i = tid; i < dim * vs; i += blockDim.x) S[i] = pos0 > 0 ? st[i] : 0.0f;
+  float m = pos0 > 0 ? st[(size_t)dim * vs] : 0.0f;            // every thread carries the scalar chain
+  const float qscale = 1.0f / sqrtf((float)dim);
+  for (int j = 0; j < cnt; ++j) {
+    const size_t t = (size_t)(start + j);
+    __syncthreads();
+    for (int k = tid; k < dim; k += blockDim.x) {
+      qs[k] = to_f(in[t * ld + col_q + h * dim + k]) * qscale;
+      ks[k] = to_f(in[t * ld + col_k + h * dim + k]);
+    }
+    const float li = cap_f(gates[t * ldg + col_i + h] + i_bias[h], cap);
+    const float lf = log_sigmoid_f(cap_f(gates[t * ldg + col_f + h] + f_bias[h], cap));
+    const float mn = fmaxf(lf + m, li);
+    const float a = expf(lf + m - mn), cc = expf(li - mn), em = expf(-mn);
+    m = mn;
+    __syncthreads();
+    for (int c = tid; c < vs; c += blockDim.x) {
+      const float v = c < vdim ? to_f(in[t * ld + col_v + h * vdim + c]) : 1.0f;
+      const float cv = cc * v;
+      float o = 0.0f;
+      for (int i = 0; i < dim; ++i) {
+        const float s = fmaf(a, S[(size_t)i * vs + c], cv * ks[i]);
+        S[(size_t)i * vs + c] = s;
+        o = fmaf(s, qs[i], o);
+      }
+      os[c] = o;
+    }
+    __syncthreads();
+    const float den = 1.0f / (fmaxf(fabsf(os[vdim]), em) + 1e-6f);
+    float o2 = 0.0f;
+    for (int c = tid; c < vdim; c += blockDim.x) { const float o = os[c] * den; o2 = fmaf(o, o, o2); }
+    o2 = block_sum(o2, red);
+    const float inv = den / sqrtf(o2 / (float)vdim + eps);
+    for (int c = tid; c < vdim; c += blockDim.x) {
+      const float gt = sigmoid_f(to_f(in[t * ld + col_g + h * vdim + c]));
+      out[t * ldo + h * vdim + c] = from_f<AT>(os[c] * inv * norm_w[h * vdim + c] * gt);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dim * vs; i += blockDim.x) st[i] = S[i];
+  if (tid == 0) st[(size_t)dim * vs] = m;
+}
+
 }  // namespace hy

@@ -9,6 +9,13 @@ and a per-channel layer scale on each sublayer.  Mixers: "mamba2" (state-space r
 "latent_attention" (attention over a shared low-rank latent with a rotated key part and a sink; a layer may use an earlier
 layer's cached latent), "hgrn2" (gated linear recurrence); routed gated experts; positions only through the rotation.
 
+Architecture "Vosolorn": the sublayers read the residual stream itself and an RMS norm with a layer scale sits on each
+sublayer's output; the embedding is normed and serves as the output head.  Mixers: "attention" (softmax attention over a
+sliding window plus one pooled key / value per block of tokens that lies wholly before the window, per-head query / key
+norms, interleaved rotary pairs, values rotated by their own position) and "mlstm" (matrix memory with capped
+exponential gates under a running maximum); feed-forward "dense" (gated, tanh-gelu) or "moe" (plain erf-gelu experts
+chosen by the largest router logits plus a bias, softmax over the chosen, beside a shared expert).
+
 Every size and every constant that can differ between models is read from config.json; sizes that only the tensors know
 (the inner sizes of the two-step decay and gate projections) are read from the checkpoint's tensor shapes."""
 from __future__ import annotations
@@ -21,10 +28,12 @@ from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 
-MIX_ATTN_SCAN, MIX_DELTA, MIX_SSD, MIX_LATENT, MIX_GLR = 0, 1, 2, 3, 4
-FF_NONE, FF_RELU2, FF_ROUTED = 0, 1, 2
-NORM_RMS_OFFSET, NORM_TANH = 0, 1
-BLOCK_PARALLEL, BLOCK_SANDWICH = 0, 1
+MIX_ATTN_SCAN, MIX_DELTA, MIX_SSD, MIX_LATENT, MIX_GLR, MIX_WINDOW, MIX_MLSTM = 0, 1, 2, 3, 4, 5, 6
+FF_NONE, FF_RELU2, FF_ROUTED, FF_GATED = 0, 1, 2, 3
+ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ROUTE_SIGMOID_GROUPS, ROUTE_TOP_SOFTMAX = 0, 1
+NORM_RMS_OFFSET, NORM_TANH, NORM_RMS = 0, 1, 2
+BLOCK_PARALLEL, BLOCK_SANDWICH, BLOCK_POSTNORM = 0, 1, 2
 POS_SINUSOID, POS_NONE = 0, 1
 _ST_DTYPES = {"BF16": (0, 2), "F32": (1, 4), "F16": (2, 2), "I32": (3, 4)}
 
@@ -89,6 +98,28 @@ class LayerSpec:
     x_groups: int = 1
     x_keep: int = 1
     x_scale: float = 1.0
+    x_route: int = ROUTE_SIGMOID_GROUPS
+    x_plain: int = 0
+    x_act: int = ACT_SILU
+    x_shared_ff: int = 0
+    ff_act: int = ACT_SILU
+    # attention over a window and pooled blocks
+    w_heads: int = 0
+    w_kv_heads: int = 0
+    w_dim: int = 0
+    w_vdim: int = 0
+    w_window: int = 1
+    w_pool: int = 1
+    w_rot_dims: int = 0
+    w_rot_values: int = 0
+    w_qk_norm: int = 0
+    w_rot_base: float = 10000.0
+    w_scale: float = 1.0
+    # matrix memory
+    t_heads: int = 0
+    t_dim: int = 0
+    t_vdim: int = 0
+    t_gate_cap: float = 0.0
 
     def cache_elems_per_token(self) -> int:
         """Elements this layer keeps in the paged cache for every token of a request."""
@@ -96,6 +127,8 @@ class LayerSpec:
             return self.a_kv_heads * self.a_dim
         if self.mixer == MIX_LATENT and self.l_kv_from < 0:
             return self.l_kv_rank + self.l_rot_dim
+        if self.mixer == MIX_WINDOW:                  # keys and values, and their pooled blocks
+            return -(-self.w_kv_heads * (self.w_dim + self.w_vdim) * (self.w_pool + 1) // self.w_pool)
         return 0
 
 
@@ -142,6 +175,33 @@ def _routed_ff(spec: LayerSpec, mlp: dict) -> None:
         raise ValueError("routed feed-forward: top exceeds the experts a token may choose from")
 
 
+def _window_spec(m: dict) -> LayerSpec:
+    rot, mask = m.get("rot") or {}, m["mask"]
+    spec = LayerSpec(MIX_WINDOW, w_heads=int(m["heads"]), w_kv_heads=int(m["kv_heads"]), w_dim=int(m["dim"]),
+                     w_vdim=int(m["vdim"]), w_window=int(mask["size"]), w_pool=int(mask["pool"]),
+                     w_rot_dims=int(rot.get("dims", 0)), w_rot_values=1 if rot else 0, w_qk_norm=1,
+                     w_rot_base=float(rot.get("base", 10000.0)), w_scale=float(m["scale"]))
+    if spec.w_kv_heads <= 0 or spec.w_heads % spec.w_kv_heads:
+        raise ValueError("attention: heads must be a multiple of kv_heads")
+    if spec.w_rot_dims % 2 or spec.w_rot_dims > spec.w_dim:
+        raise ValueError("attention: rot.dims must be even and at most dim")
+    if spec.w_rot_values and spec.w_vdim % 2:
+        raise ValueError("attention: rotated values need an even vdim")
+    if spec.w_window < 1 or spec.w_pool < 1:
+        raise ValueError("attention: mask.size and mask.pool must be at least 1")
+    return spec
+
+
+def _plain_experts_ff(spec: LayerSpec, mlp: dict) -> None:
+    r = mlp["router"]
+    spec.ff_kind, spec.ff = FF_ROUTED, int(mlp["expert"]["ff"])
+    spec.x_experts, spec.x_top = int(r["experts"]), int(r["top"])
+    spec.x_route, spec.x_plain, spec.x_act = ROUTE_TOP_SOFTMAX, 1, ACT_GELU_ERF
+    spec.x_shared_ff = int(mlp["shared"]["ff"]) if mlp.get("shared") else 0
+    if not 1 <= spec.x_top <= spec.x_experts:
+        raise ValueError("mixture of experts: top must lie in 1..experts")
+
+
 @dataclass
 class HybridConfig:
     architecture: str
@@ -154,6 +214,8 @@ class HybridConfig:
     norm_kind: int = NORM_RMS_OFFSET
     block_kind: int = BLOCK_PARALLEL
     pos_kind: int = POS_SINUSOID
+    embed_norm: bool = False
+    tied_head: bool = False
     # what the engine's configuration reads from a model description
     max_position_embeddings: int = 1 << 30          # positions enter through a sinusoid or a rotation: no table to run out of
     is_hybrid: bool = True
@@ -167,6 +229,8 @@ class HybridConfig:
         """cfg: the parsed config.json; shapes: tensor name -> shape (needed by channel_delta layers)."""
         if cfg.get("architecture") == "Famepel":
             return cls._famepel(cfg)
+        if cfg.get("architecture") == "Vosolorn":
+            return cls._vosolorn(cfg)
         layers = []
         for i, lc in enumerate(cfg["layers"]):
             m = lc["mixer"]
@@ -219,6 +283,31 @@ class HybridConfig:
         return cls(architecture="Famepel", width=int(cfg["width"]), vocab=int(cfg["vocab"]),
                    emb_scale=float(cfg["embedding"]["scale"]), logit_scale=1.0, norm_eps=float(cfg["norm"]["eps"]),
                    layers=layers, norm_kind=NORM_TANH, block_kind=BLOCK_SANDWICH, pos_kind=POS_NONE)
+
+    @classmethod
+    def _vosolorn(cls, cfg: dict) -> "HybridConfig":
+        layers: List[LayerSpec] = []
+        for lc in cfg["layers"]:
+            kind, m = lc["type"], lc["mixer"]
+            if kind == "attention":
+                spec = _window_spec(m)
+            elif kind == "mlstm":
+                spec = LayerSpec(MIX_MLSTM, t_heads=int(m["heads"]), t_dim=int(m["dim"]), t_vdim=int(m["vdim"]),
+                                 t_gate_cap=float(m["gate_cap"]))
+            else:
+                raise NotImplementedError(f"layer type {kind!r}")
+            mlp = lc.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") == "dense":
+                    spec.ff_kind, spec.ff, spec.ff_act = FF_GATED, int(mlp["ff"]), ACT_GELU_TANH
+                elif mlp.get("kind") == "moe":
+                    _plain_experts_ff(spec, mlp)
+                else:
+                    raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
+            layers.append(spec)
+        return cls(architecture="Vosolorn", width=int(cfg["width"]), vocab=int(cfg["vocab"]), emb_scale=1.0,
+                   logit_scale=float(cfg.get("logit_scale", 1.0)), norm_eps=float(cfg["norm"]["eps"]), layers=layers,
+                   norm_kind=NORM_RMS, block_kind=BLOCK_POSTNORM, pos_kind=POS_NONE, embed_norm=True, tied_head=True)
 
     @classmethod
     def from_dir(cls, path: str) -> "HybridConfig":

@@ -39,7 +39,8 @@ class HybridRuntime:
         self.max_pages_per_seq = max_pages_per_seq
         self.max_want = max_want or max_step_tokens
         m = cabi.ModelCfg(config.width, config.vocab, len(config.layers), DTYPES[dtype], config.emb_scale,
-                          config.logit_scale, config.norm_eps, config.norm_kind, config.block_kind, config.pos_kind)
+                          config.logit_scale, config.norm_eps, config.norm_kind, config.block_kind, config.pos_kind,
+                          int(config.embed_norm), int(config.tied_head))
         layers = (cabi.LayerCfg * len(config.layers))()
         for i, s in enumerate(config.layers):
             for name, _ in cabi.LayerCfg._fields_:

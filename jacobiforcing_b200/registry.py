@@ -40,6 +40,7 @@ FAMILIES: Dict[str, ModelFamily] = {
     "Qwen3ForCausalLM": ModelFamily("qwen2", False, _qwen2_config, _qwen2_runner),
     "Kinetar": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
     "Famepel": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
+    "Vosolorn": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
 }
 
 
