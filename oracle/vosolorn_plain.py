@@ -208,7 +208,7 @@ def tensor_shapes(config: dict) -> Dict[str, tuple]:
 
 
 def random_weights(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
-    """Random bf16-representable weights (returned as fp32): matrices ~ N(0, 1/in), norm weights and layer scales near
+    """Random bf16 weights: matrices ~ N(0, 1/in), norm weights and layer scales near
     one, gate biases that keep the forget gate open, router biases of the size of the logits."""
     g = torch.Generator().manual_seed(seed)
     out = {}
@@ -228,5 +228,5 @@ def random_weights(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             t = 0.5 + torch.rand(shape, generator=g)
         else:
             t = 1.0 + 0.2 * torch.randn(shape, generator=g)
-        out[name] = t.to(torch.bfloat16).to(torch.float32)
+        out[name] = t.to(torch.bfloat16)
     return out
