@@ -506,6 +506,32 @@ def run_compare_famepel(args):
                       "peaks": peaks, "clocks": clocks, "results": res}))
 
 
+def run_compare_vosolorn(args):
+    """Option --compare-vosolorn: Vosolorn (matrix memory / window attention with pooled blocks, gated dense feed-forward
+    and expert mixture) beside the closest existing model, Famepel, at equal width and depth; device times from CUDA
+    events, three warm-up passes, weights + activations larger than L2."""
+    import __graft_entry__ as g
+    g.build()
+    from jacobiforcing_b200 import hybrid_bench as hb
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        peaks = {"hbm_gbs": float(mp["hbm_gbs"]), "bf16_tflops": float(mp["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    mon = ClockSampler(0)
+    mon.start()
+    res = []
+    for size in args.compare_vosolorn.split(","):
+        row = {"size": size}
+        row["vosolorn"] = hb.run_hybrid(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks, design="Vosolorn")
+        row["famepel"] = hb.run_hybrid(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks, design="Famepel")
+        res.append(row)
+    clocks = mon.stop()
+    print(json.dumps({"metric": "vosolorn_vs_famepel_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "peaks": peaks, "clocks": clocks, "results": res}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -536,6 +562,9 @@ def main():
     ap.add_argument("--compare-famepel", default="", metavar="SIZES",
                     help="instead of the headline workload: prefill / decode throughput of Famepel beside the Kinetar hybrid "
                          "decoder at equal size, e.g. w1024,w2048 (one JSON line)")
+    ap.add_argument("--compare-vosolorn", default="", metavar="SIZES",
+                    help="instead of the headline workload: prefill / decode throughput of Vosolorn beside Famepel at equal "
+                         "size, e.g. w1024,w2048 (one JSON line)")
     ap.add_argument("--hybrid-prompt", type=int, default=4096)
     ap.add_argument("--hybrid-decode-steps", type=int, default=35)
     args = ap.parse_args()
@@ -544,6 +573,9 @@ def main():
         return
     if args.compare_famepel:
         run_compare_famepel(args)
+        return
+    if args.compare_vosolorn:
+        run_compare_vosolorn(args)
         return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3                                  # timing rule: at least three warm-up steps

@@ -863,6 +863,7 @@ extern "C" int hy_finalize(hy_handle h) {
     int maxH = 0, maxG = 0, maxD = 0;
     for (auto& c : h->lc) {
       if (c.mixer == HY_MIX_ATTN_SCAN) { maxH = std::max(maxH, c.a_heads); maxG = std::max(maxG, c.a_kv_heads); maxD = std::max(maxD, c.a_dim); }
+      if (c.mixer == HY_MIX_WINDOW) { maxH = std::max(maxH, c.w_heads); maxG = std::max(maxG, c.w_kv_heads); maxD = std::max(maxD, 8); }
       if (c.mixer == HY_MIX_LATENT) {
         maxH = std::max(maxH, c.l_heads); maxG = std::max(maxG, 1);
         maxD = std::max(maxD, std::max(c.l_kv_rank + c.l_rot_dim, c.l_kv_rank <= 128 ? 128 : c.l_kv_rank <= 256 ? 256 : 512));
@@ -1000,6 +1001,25 @@ bool attn_units(hy_engine* h, int E, int T, int H, int G, bool any_ratio = false
   return true;
 }
 
+
+// Work units of the tensor-core window attention: (entry, key head, tile of 64 rows), late tiles first (they see the most).
+bool window_units(hy_engine* h, int E, int H, int G) {
+  const int R = H / G;
+  if (h->units_n > 0 && h->units_H == H && h->units_G == G && h->units_split == -1) return true;
+  if (h->units_n > 0) cudaStreamSynchronize(h->stream);        // another layout earlier in this step still reads the list
+  size_t n = 0;
+  for (int e = 0; e < E; ++e) {
+    const int rows = (h->step_start[e + 1] - h->step_start[e]) * R;
+    for (int g = 0; g < G; ++g)
+      for (int row0 = (rows - 1) / 64 * 64; row0 >= 0; row0 -= 64) {
+        if (n >= h->units_cap) return false;
+        h->units_h[n++] = AttnUnit{e, g, row0, 0};
+      }
+  }
+  cudaMemcpyAsync(h->units_d, h->units_h, n * sizeof(AttnUnit), cudaMemcpyHostToDevice, h->stream);
+  h->units_n = (int)n; h->units_H = H; h->units_G = G; h->units_split = -1; h->units_ns = 1;
+  return true;
+}
 
 // One layer of a norm - sublayer - norm model:  x += ls1 * n1b(mixer(n1(x)));  x += ls2 * n2b(experts(n2(x))).
 // The output norms are element-wise, so they run in the epilogue of the mixer's output projection and in the experts'
@@ -1288,9 +1308,23 @@ int postnorm_layer(hy_engine* h, const Batch& b, size_t li) {
     }
     {
       ProfScope ps(h, HY_PROF_ATTN);
-      window_attn_kernel<AT, AT><<<(T * c.w_heads + 3) / 4, 128, 4 * c.w_dim * sizeof(float), s>>>(
-          b, cv, h->ld_cv, wc, (const AT*)L.cache, (const AT*)L.cache_v, (const AT*)L.pool_k, (const AT*)L.pool_v, h->f1, h->ld_f1, cat,
-          h->ld_cat);
+      bool tc = false;
+      if constexpr (std::is_same<AT, bf16>::value) {
+        // head sizes that are multiples of 8 up to 128: tensor-core tiles of 64 rows x 64 keys
+        if (c.w_dim % 8 == 0 && c.w_vdim % 8 == 0 && c.w_dim <= 128 && c.w_vdim <= 128 && h->units_d &&
+            window_units(h, E, c.w_heads, c.w_kv_heads)) {
+          tc = true;
+#define HY_WIN_ARGS b, h->units_d, cv, h->ld_cv, wc, (const bf16*)L.cache, (const bf16*)L.cache_v, (const bf16*)L.pool_k, \
+          (const bf16*)L.pool_v, h->f1, h->ld_f1, cat, h->ld_cat
+          if (c.w_dim <= 64 && c.w_vdim <= 64) window_mma_kernel<64><<<h->units_n, 128, 0, s>>>(HY_WIN_ARGS);
+          else window_mma_kernel<128><<<h->units_n, 128, 0, s>>>(HY_WIN_ARGS);
+#undef HY_WIN_ARGS
+        }
+      }
+      if (!tc)
+        window_attn_kernel<AT, AT><<<(T * c.w_heads + 3) / 4, 128, 4 * c.w_dim * sizeof(float), s>>>(
+            b, cv, h->ld_cv, wc, (const AT*)L.cache, (const AT*)L.cache_v, (const AT*)L.pool_k, (const AT*)L.pool_v, h->f1, h->ld_f1,
+            cat, h->ld_cat);
       h->launches++;
     }
   } else {

@@ -22,6 +22,7 @@
 #pragma once
 #include "hy_kernels.cuh"
 #include "hy_mixers.cuh"
+#include "hy_attn.cuh"
 
 namespace hy {
 
@@ -189,6 +190,195 @@ __global__ void __launch_bounds__(128) window_attn_kernel(Batch b, const AT* __r
         y = (d & 1) ? fmaf(y, co, -o * si) : fmaf(y, co, o * si);                    // the turn by minus the position
       }
       out[(size_t)t * ldo + h * c.vdim + d] = from_f<OT>(y);
+    }
+  }
+}
+
+// ---- the same attention on tensor cores (bf16 build) ----------------------------------------------------------------------------
+// Work unit = (entry, key head, tile of 64 query rows); rows are (token, query head of the group) pairs, token-major, so
+// the heads that share a key head share every tile that is loaded.  A unit walks the pooled blocks any of its rows may
+// see (tiles of 64 blocks), then the tokens from the first window of the tile to its last position (tiles of 64 keys
+// aligned to absolute positions); each row masks what it does not see.  S = Q K^T by mma.sync m16n8k16 (bf16 operands,
+// fp32 accumulators), online softmax in fp32, O += P V with P split into a bf16 head and a bf16 remainder (the weights
+// stay 32-bit in effect).  Key and value rows are zero-padded to DP columns in shared memory (dim, vdim multiples of 8, at
+// most DP).  The output is normalised, turned back by the query's position and written as the operand of the output
+// projection: no key splits, since a row sees at most window + position / pool rows.
+template <int DP>
+__global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit* __restrict__ units, const bf16* __restrict__ q,
+                                                         int ldq, WindowCfg c, const bf16* __restrict__ kc,
+                                                         const bf16* __restrict__ vc, const bf16* __restrict__ kp,
+                                                         const bf16* __restrict__ vp, const float* __restrict__ vrot, int ldv,
+                                                         bf16* __restrict__ out, int ldo) {
+  constexpr int LD = DP + 8;                            // padded row (elements): ldmatrix rows fall into distinct banks
+  __shared__ __align__(16) bf16 ks[64 * LD];
+  __shared__ __align__(16) bf16 vs[64 * LD];            // the query tile first, value tiles afterwards
+  const AttnUnit u = units[blockIdx.x];
+  const int R = c.H / c.G;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int start = b.ent_start[u.entry], cnt = b.ent_start[u.entry + 1] - start, pos0 = b.ent_pos0[u.entry];
+  const int rows_total = cnt * R;
+  const int* pg = b.pages + (size_t)u.entry * b.max_pages;
+  const int kchunks = c.dim / 8, vchunks = c.vdim / 8, slots = window_block_slots(b.page_size, c.pool);
+  for (int i = tid; i < 64 * (DP / 8); i += 128) {
+    const int r = i / (DP / 8), ch = i % (DP / 8);
+    const int row = u.row0 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows_total && ch < kchunks)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(start + row / R) * ldq + (u.kv_head * R + row % R) * c.dim + ch * 8);
+    *reinterpret_cast<uint4*>(&vs[r * LD + ch * 8]) = v;
+  }
+  __syncthreads();
+  uint32_t qa[DP / 16][4];
+  {
+    const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk)
+      jf::ldmatrix_x4(jf::smem_u32(&vs[r * LD + kk * 16 + (lane >> 4) * 8]), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+  }
+  const int r_lo = u.row0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const bool v_lo = r_lo < rows_total, v_hi = r_hi < rows_total;
+  const int p_lo = v_lo ? pos0 + r_lo / R : -1, p_hi = v_hi ? pos0 + r_hi / R : -1;
+  const int nb_lo = p_lo - c.window + 1 > 0 ? (p_lo - c.window + 1) / c.pool : 0;
+  const int nb_hi = p_hi - c.window + 1 > 0 ? (p_hi - c.window + 1) / c.pool : 0;
+  const bool warp_live = (u.row0 + warp * 16) < rows_total;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+  float o[DP / 8][4];
+#pragma unroll
+  for (int i = 0; i < DP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+  const int last_row = min(u.row0 + 63, rows_total - 1);
+  const int p_first = pos0 + u.row0 / R, p_last = pos0 + last_row / R;
+  const int nb_tile = p_last - c.window + 1 > 0 ? (p_last - c.window + 1) / c.pool : 0;       // blocks the tile's last row sees
+  const int tok0 = max(0, p_first - c.window + 1) / 64 * 64;                                    // first token tile
+  const int n_pool_tiles = (nb_tile + 63) / 64;
+  const int n_tiles = n_pool_tiles + (p_last / 64 - tok0 / 64 + 1);
+  for (int it = 0; it < n_tiles; ++it) {
+    const bool pooled = it < n_pool_tiles;
+    const int j0 = pooled ? it * 64 : tok0 + (it - n_pool_tiles) * 64;
+    const int j_end = pooled ? nb_tile : p_last + 1;
+    __syncthreads();                                     // the previous tiles (or the query tile) have been read
+    for (int i = tid; i < 64 * (DP / 8); i += 128) {
+      const int r = i / (DP / 8), ch = i % (DP / 8);
+      const int j = j0 + r;
+      const bool ok = j < j_end;
+      const int jj = ok ? j : j0;
+      size_t rowi;
+      if (pooled) {
+        const int first = jj * c.pool;
+        rowi = ((size_t)pg[first / b.page_size] * c.G + u.kv_head) * slots + (first % b.page_size) / c.pool;
+      } else {
+        rowi = ((size_t)pg[jj / b.page_size] * c.G + u.kv_head) * b.page_size + jj % b.page_size;
+      }
+      const bool kok = ok && ch < kchunks, vok = ok && ch < vchunks;
+      jf::cp_async_16(&ks[r * LD + ch * 8], (pooled ? kp : kc) + rowi * c.dim + (kok ? ch * 8 : 0), kok ? 16u : 0u);
+      jf::cp_async_16(&vs[r * LD + ch * 8], (pooled ? vp : vc) + rowi * c.vdim + (vok ? ch * 8 : 0), vok ? 16u : 0u);
+    }
+    jf::cp_async_commit();
+    jf::cp_async_wait_all();
+    __syncthreads();
+    if (!warp_live) continue;
+    float s[8][4];
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f; }
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk) {
+      if (kk * 16 >= c.dim) continue;
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b0, b1, b2, b3;
+        const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
+        jf::ldmatrix_x4(jf::smem_u32(&ks[key * LD + kk * 16 + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
+        jf::mma_bf16_16816(s[np * 2], qa[kk], b0, b1);
+        jf::mma_bf16_16816(s[np * 2 + 1], qa[kk], b2, b3);
+      }
+    }
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int j = j0 + nb * 8 + (lane & 3) * 2 + cc;
+        const bool see_lo = pooled ? j < nb_lo : (j <= p_lo && j > p_lo - c.window);
+        const bool see_hi = pooled ? j < nb_hi : (j <= p_hi && j > p_hi - c.window);
+        s[nb][cc] = see_lo ? s[nb][cc] * c.scale : -INFINITY;
+        s[nb][2 + cc] = see_hi ? s[nb][2 + cc] * c.scale : -INFINITY;
+        mx_lo = fmaxf(mx_lo, s[nb][cc]);
+        mx_hi = fmaxf(mx_hi, s[nb][2 + cc]);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float ref_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
+    const float c_lo = expf(m_lo - ref_lo), c_hi = expf(m_hi - ref_hi);      // m = -inf: exp(-inf) = 0
+    m_lo = mn_lo; m_hi = mn_hi;
+    float sum_lo = 0.0f, sum_hi = 0.0f;
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        s[nb][cc] = expf(s[nb][cc] - ref_lo);
+        s[nb][2 + cc] = expf(s[nb][2 + cc] - ref_hi);
+        sum_lo += s[nb][cc];
+        sum_hi += s[nb][2 + cc];
+      }
+    }
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+    l_lo = l_lo * c_lo + sum_lo;
+    l_hi = l_hi * c_hi + sum_hi;
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) { o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi; }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {                     // 16 keys per step
+      uint32_t ph[4], pl[4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const float* sv = s[kk * 2 + half];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+          const float x0 = sv[rr * 2], x1 = sv[rr * 2 + 1];
+          const float h0 = jf::bf16_round(x0), h1 = jf::bf16_round(x1);
+          ph[half * 2 + rr] = jf::pack_bf16x2(h0, h1);
+          pl[half * 2 + rr] = jf::pack_bf16x2(x0 - h0, x1 - h1);
+        }
+      }
+#pragma unroll
+      for (int np = 0; np < DP / 16; ++np) {
+        if (np * 16 >= c.vdim) continue;
+        uint32_t b0, b1, b2, b3;
+        const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        jf::ldmatrix_x4_trans(jf::smem_u32(&vs[key * LD + np * 16 + (lane >> 4) * 8]), b0, b1, b2, b3);
+        jf::mma_bf16_16816(o[np * 2], ph, b0, b1);
+        jf::mma_bf16_16816(o[np * 2], pl, b0, b1);
+        jf::mma_bf16_16816(o[np * 2 + 1], ph, b2, b3);
+        jf::mma_bf16_16816(o[np * 2 + 1], pl, b2, b3);
+      }
+    }
+  }
+  if (!warp_live) return;
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int row = hh ? r_hi : r_lo;
+    if (row >= rows_total) continue;
+    const int t = start + row / R, h = u.kv_head * R + row % R;
+    const float inv = 1.0f / (hh ? l_hi : l_lo);
+    bf16* po = out + (size_t)t * ldo + h * c.vdim;
+    const float* vr = vrot + (size_t)t * ldv;
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) {
+      const int d = i * 8 + (lane & 3) * 2;                // an even dimension: the pair (d, d + 1) sits in this thread
+      if (d >= c.vdim) continue;
+      float y0 = o[i][hh * 2] * inv, y1 = o[i][hh * 2 + 1] * inv;
+      if (c.rot_values) {
+        const float co = vr[d], si = vr[d + 1];
+        const float a0 = fmaf(y0, co, y1 * si), a1 = fmaf(y1, co, -y0 * si);          // the turn by minus the position
+        y0 = a0; y1 = a1;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(po + d) = __floats2bfloat162_rn(y0, y1);
     }
   }
 }

@@ -2,7 +2,9 @@
 tokens/s, device time per kernel group with its distance from the roofline (tensor peak for prefill products, HBM
 bandwidth for decode).  Random weights, synthetic tokens.  `bench.py --compare-hybrid`: Kinetar beside the Qwen2 engine at
 equal width / depth / feed-forward size.  `bench.py --compare-famepel`: Famepel beside Kinetar at equal width / depth and
-equal ACTIVE feed-forward size per token (top x expert size = the dense size)."""
+equal ACTIVE feed-forward size per token (top x expert size = the dense size).  `bench.py --compare-vosolorn`: Vosolorn
+beside Famepel at equal width / depth (both are normed-sublayer designs with layer scales, a matrix-state recurrence,
+attention and routed experts)."""
 from __future__ import annotations
 
 import time
@@ -146,11 +148,90 @@ def famepel_weights(desc: dict, seed: int) -> Dict[str, np.ndarray]:
     return w
 
 
-def _famepel_costs(desc: dict, hc) -> dict:
+def vosolorn_description(sz: dict) -> dict:
+    """Layers in the order matrix memory, matrix memory, window attention, matrix memory; feed-forwards alternate between
+    the gated dense layer and the expert mixture.  Matrix memory in heads of 64 keys x 128 values (values = width), attention
+    in heads of 128 over a window of 1024 tokens and pooled blocks of 16, half of each head rotated; experts of ff / top
+    each (8 x top of them, `top` per token) beside a shared expert of the same size."""
+    W, top = sz["width"], sz.get("top", 4)
+    ffe = sz["ff"] // top
+    moe = {"kind": "moe", "expert": {"ff": ffe}, "router": {"experts": 8 * top, "top": top}, "shared": {"ff": ffe}}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    mem = {"heads": W // 128, "dim": 64, "vdim": 128, "gate_cap": 15.0}
+    att = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": 1024, "pool": 16},
+           "rot": {"base": 1e6, "dims": 64}, "scale": 128 ** -0.5}
+    layers = []
+    for i in range(sz["layers"]):
+        kind = "attention" if i % 4 == 2 else "mlstm"
+        layers.append({"type": kind, "mixer": att if kind == "attention" else mem, "mlp": moe if i % 2 else dense})
+    return {"architecture": "Vosolorn", "layers": layers, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "vocab": sz["vocab"], "width": W}
+
+
+def vosolorn_weights(desc: dict, seed: int) -> Dict[str, np.ndarray]:
+    rng = np.random.default_rng(seed)
+    W, V = desc["width"], desc["vocab"]
+
+    def lin(n, k):
+        return (rng.standard_normal((n, k), dtype=np.float32) / np.sqrt(k)).astype(np.float32)
+
+    def vec(n, s=0.1, b=0.0):
+        return (rng.standard_normal(n, dtype=np.float32) * s + b).astype(np.float32)
+    w = {"embed": lin(V, W) * 4.0, "embed.norm": vec(W, 0.1, 1.0), "final.norm": vec(W, 0.1, 1.0)}
+    for i, lc in enumerate(desc["layers"]):
+        p, m, M = f"l{i}.", lc["mixer"], f"l{i}.mix."
+        w[p + "norm1"], w[p + "ls1"] = vec(W, 0.1, 1.0), vec(W, 0.1, 0.7)
+        if lc["type"] == "attention":
+            H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            w.update({M + "q": lin(H * D, W), M + "k": lin(G * D, W), M + "v": lin(G * Dv, W), M + "q.norm": vec(D, 0.1, 1.0),
+                      M + "k.norm": vec(D, 0.1, 1.0), M + "o": lin(W, H * Dv)})
+        else:
+            H, nq, nv = m["heads"], m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            w.update({M + "q": lin(nq, W), M + "k": lin(nq, W), M + "v": lin(nv, W), M + "g": lin(nv, W), M + "o": lin(W, nv),
+                      M + "norm": vec(nv, 0.1, 1.0), M + "i": lin(H, W), M + "i.b": vec(H, 0.5), M + "f": lin(H, W),
+                      M + "f.b": vec(H, 0.5, 3.0)})
+        mlp = lc["mlp"]
+        w[p + "norm2"], w[p + "ls2"] = vec(W, 0.1, 1.0), vec(W, 0.1, 0.7)
+        if mlp["kind"] == "dense":
+            w.update({p + "mlp.gate": lin(mlp["ff"], W), p + "mlp.up": lin(mlp["ff"], W), p + "mlp.down": lin(W, mlp["ff"])})
+        else:
+            ff, E = mlp["expert"]["ff"], mlp["router"]["experts"]
+            w[p + "mlp.router"], w[p + "mlp.router.b"] = lin(E, W) * 2.0, vec(E, 0.3)
+            for e in range(E):
+                w[f"{p}mlp.e{e}.up"], w[f"{p}mlp.e{e}.down"] = lin(ff, W), lin(W, ff)
+            w[p + "mlp.shared.up"], w[p + "mlp.shared.down"] = lin(mlp["shared"]["ff"], W), lin(W, mlp["shared"]["ff"])
+    return w
+
+
+def _vosolorn_costs(desc: dict, hc, prompt: int) -> dict:
+    """Multiply-adds per token per kernel group (the dense feed-forward counts under gemm_in / gemm_out, where its products
+    run); for attention the multiply-adds of one whole prompt, for the recurrence those of one token."""
+    W = desc["width"]
+    per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0, "experts": 0, "expert_weights": 0, "delta": 0, "attention_prompt": 0}
+    for s in hc.layers:
+        if s.mixer == 5:
+            per["gemm_in"] += (s.w_heads * s.w_dim + s.w_kv_heads * (s.w_dim + s.w_vdim)) * W
+            per["gemm_out"] += s.w_heads * s.w_vdim * W
+            seen = sum(min(i + 1, s.w_window) + max(0, (i - s.w_window + 1) // s.w_pool) for i in range(prompt))
+            per["attention_prompt"] += seen * s.w_heads * (s.w_dim + s.w_vdim)
+        else:
+            per["gemm_in"] += (2 * s.t_heads * s.t_dim + 2 * s.t_heads * s.t_vdim + 2 * s.t_heads) * W
+            per["gemm_out"] += s.t_heads * s.t_vdim * W
+            per["delta"] += 2 * s.t_heads * s.t_dim * (s.t_vdim + 1)
+        if s.ff_kind == 3:
+            per["gemm_in"] += 2 * s.ff * W
+            per["gemm_out"] += s.ff * W
+        elif s.ff_kind == 2:
+            per["experts"] += (s.x_top * s.ff + s.x_shared_ff) * 2 * W
+            per["expert_weights"] += (s.x_experts * s.ff + s.x_shared_ff) * 2 * W
+    per["head"] = desc["vocab"] * W
+    return per
+
+
+def _famepel_costs(desc: dict, hc, prompt: int = 0) -> dict:
     """Multiply-adds per token per kernel group; for the experts both the work of a token (its `top` experts) and the
     weights of ALL experts (what a long prefill streams once per step)."""
     W = desc["width"]
-    per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0, "experts": 0, "expert_weights": 0}
+    per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0, "experts": 0, "expert_weights": 0, "delta": 0, "attention_prompt": 0}
     for s in hc.layers:
         if s.mixer == 2:
             inner = s.m_heads * s.m_vdim
@@ -161,9 +242,11 @@ def _famepel_costs(desc: dict, hc) -> dict:
             per["gemm_in"] += (s.l_q_rank + (s.l_kv_rank + s.l_rot_dim if own else 0)) * W
             per["gemm_out"] += s.l_heads * s.l_vdim * W
             per["small_gemm"] += s.l_heads * ((s.l_dim + s.l_rot_dim) * s.l_q_rank + s.l_dim * s.l_kv_rank + s.l_vdim * s.l_kv_rank)
+            per["attention_prompt"] += prompt * (prompt + 1) // 2 * s.l_heads * (2 * s.l_kv_rank + s.l_rot_dim)
         else:
             per["gemm_in"] += (2 * s.g_heads * s.g_dim + s.g_heads * s.g_vdim) * W
             per["gemm_out"] += s.g_heads * s.g_vdim * W
+            per["delta"] += 2 * s.g_heads * s.g_dim * s.g_vdim
         if s.ff_kind == 2:
             per["experts"] += s.x_top * 3 * s.ff * W
             per["expert_weights"] += s.x_experts * 3 * s.ff * W
@@ -171,10 +254,12 @@ def _famepel_costs(desc: dict, hc) -> dict:
     return per
 
 
-def _hybrid_costs(desc: dict, hc) -> dict:
+def _hybrid_costs(desc: dict, hc, prompt: int = 0) -> dict:
     """Multiply-add FLOPs per token and weight bytes per kernel group (bf16 weights)."""
     if desc["architecture"] == "Famepel":
-        return _famepel_costs(desc, hc)
+        return _famepel_costs(desc, hc, prompt)
+    if desc["architecture"] == "Vosolorn":
+        return _vosolorn_costs(desc, hc, prompt)
     W = desc["width"]
     per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0}
     for s in hc.layers:
@@ -202,6 +287,9 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
     if design == "Famepel":
         desc = famepel_description(sz)
         w = famepel_weights(desc, seed)
+    elif design == "Vosolorn":
+        desc = vosolorn_description(sz)
+        w = vosolorn_weights(desc, seed)
     else:
         desc = hybrid_description(sz)
         w = hybrid_weights(desc, seed)
@@ -216,7 +304,7 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
     rng = np.random.default_rng(seed + 1)
     # every request decodes its own token stream (routed layers would otherwise send all of a batch to the same experts)
     toks_all = [rng.integers(0, sz["vocab"], prompt + decode_steps + 1).tolist() for _ in range(maxb)]
-    costs = _hybrid_costs(desc, hc)
+    costs = _hybrid_costs(desc, hc, prompt)
     out = {"size": size, "description": {k: sz[k] for k in sz}, "memory": rt.memory_info()}
 
     def prefill(slot):
@@ -244,6 +332,12 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
     for g in ("gemm_in", "gemm_out") + (("experts",) if costs.get("experts") else ()):
         t = prof[g] / 3 * 1e-3
         tf[g] = {"tflops": 2.0 * costs[g] * prompt / t / 1e12, "of_measured_bf16_peak": 2.0 * costs[g] * prompt / t / 1e12 / peaks["bf16_tflops"]}
+    # the mixers' own kernels: achieved multiply-add rate (a recurrence runs on the fp32 pipes, attention here too or on
+    # mma.sync); the two designs' figures stand side by side in the comparison
+    if costs.get("delta") and prof.get("delta"):
+        tf["recurrence"] = {"tflops": 2.0 * costs["delta"] * prompt / (prof["delta"] / 3 * 1e-3) / 1e12}
+    if costs.get("attention_prompt") and prof.get("attention"):
+        tf["attention"] = {"tflops": 2.0 * costs["attention_prompt"] / (prof["attention"] / 3 * 1e-3) / 1e12}
     out["prefill"]["roofline"] = tf
     out["decode"] = {}
     for B in batches:
@@ -272,7 +366,7 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
             t = prof["experts"] / n * 1e-3
             roof["experts"] = {"gb_per_s_if_no_expert_is_shared": 2.0 * costs["experts"] * B / t / 1e9,
                                "of_measured_hbm": min(2.0 * costs["experts"] * B, 2.0 * costs["expert_weights"]) / t / 1e9 / peaks["hbm_gbs"]}
-        wbytes = 2.0 * sum(v for k, v in costs.items() if k != "expert_weights")
+        wbytes = 2.0 * sum(v for k, v in costs.items() if k not in ("expert_weights", "delta", "attention_prompt"))
         out["decode"][f"batch{B}"] = {"ms_per_step": ms / n, "tokens_per_s": B * n / ms * 1e3, "e2e_tokens_per_s": B * n / wall,
                                       "ms_by_group": {k: v / n for k, v in prof.items()}, "roofline": roof,
                                       "weights_over_time_of_measured_hbm": wbytes / (ms / n * 1e-3) / 1e9 / peaks["hbm_gbs"]}
