@@ -215,7 +215,8 @@ extern "C" int hy_create(const hy_model_cfg* model, const hy_layer_cfg* layers, 
       if (c.w_rot_values && c.w_vdim % 2) return bad("rotated values need an even vdim");
     } else if (c.mixer == HY_MIX_MLSTM) {
       if (c.t_heads <= 0 || c.t_dim <= 0 || c.t_vdim <= 0) return bad("matrix memory sizes must be positive");
-      if (((size_t)c.t_dim * (c.t_vdim + 1) + 2 * c.t_dim + c.t_vdim + 40) * 4 > 200 * 1024 && (c.t_dim > 128 || c.t_vdim > 255))
+      if (((size_t)c.t_dim * (c.t_vdim + 1) + 2 * c.t_dim + c.t_vdim + 40) * 4 > 200 * 1024 &&
+          (c.t_dim > 128 || c.t_vdim > 255))
         return bad("matrix memory: the state of one head exceeds shared memory");
     } else {
       return bad("unknown mixer kind");
@@ -1338,21 +1339,29 @@ int postnorm_layer(hy_engine* h, const Batch& b, size_t li) {
     ProfScope ps(h, HY_PROF_DELTA);
     static bool attr = false;
     if (!attr) {
-      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      cudaFuncSetAttribute(mlstm_reg_kernel<AT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
       cudaFuncSetAttribute(mlstm_kernel<AT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
       attr = true;
     }
-#define HY_MLSTM_ARGS b, pin, h->ld_pin, L.c_q, L.c_k, L.c_v, L.c_g, h->f1, h->ld_f1, 0, H, L.t_ib, L.t_fb, L.t_norm, H, dk, dv, \
+#define HY_MLSTM_GEN_ARGS b, pin, h->ld_pin, L.c_q, L.c_k, L.c_v, L.c_g, h->f1, h->ld_f1, 0, H, L.t_ib, L.t_fb, L.t_norm, H, dk, dv, \
     c.t_gate_cap, eps, L.rec_state, cat, h->ld_cat
+#define HY_MLSTM_ARGS b, pin, h->ld_pin, L.c_q, L.c_k, L.c_v, L.c_g, h->f1, h->ld_f1, 0, H, L.t_ib, L.t_fb, L.t_norm, H, dk, dv, \
+    c.t_gate_cap, eps, async_ok, L.rec_state, cat, h->ld_cat
     const int nthr = ((dv + 1 + 31) / 32) * 32;               // one thread per value column and one for the normaliser
-    auto msm = [](int dr, int nt) { return (size_t)(HY_MLSTM_TB * (2 * dr + 2 * nt) + 5 * HY_MLSTM_TB + 4) * 4; };
-    if (dk <= 32 && nthr <= 512) mlstm_reg_kernel<AT, 32><<<dim3(H, E), nthr, msm(32, nthr), s>>>(HY_MLSTM_ARGS);
-    else if (dk <= 64 && nthr <= 512) mlstm_reg_kernel<AT, 64><<<dim3(H, E), nthr, msm(64, nthr), s>>>(HY_MLSTM_ARGS);
-    else if (dk <= 128 && nthr <= 256) mlstm_reg_kernel<AT, 128><<<dim3(H, E), nthr, msm(128, nthr), s>>>(HY_MLSTM_ARGS);
-    else mlstm_kernel<AT><<<dim3(H, E), 256, ((size_t)dk * (dv + 1) + 2 * dk + dv + 1 + 40) * 4, s>>>(HY_MLSTM_ARGS);
+    // rows of q, k, v, g that start and end on 16-byte boundaries may travel by asynchronous copies
+    const int ch = 16 / (int)sizeof(AT);
+    const int async_ok = (dk % ch == 0 && dv % ch == 0 && h->ld_pin % ch == 0 && L.c_k % ch == 0 && L.c_v % ch == 0 && L.c_g % ch == 0) ? 1 : 0;
+    auto msm = [](int dr, int nt) {
+      return (size_t)(HY_MLSTM_TB * (2 * dr + 3 * nt) + 9 * HY_MLSTM_TB + 4) * 4 + (size_t)2 * HY_MLSTM_TB * (2 * dr + 2 * nt) * sizeof(AT);
+    };
+    if (dk <= 32 && nthr <= 256 && msm(32, nthr) <= 220 * 1024) mlstm_reg_kernel<AT, 32><<<dim3(H, E), nthr, msm(32, nthr), s>>>(HY_MLSTM_ARGS);
+    else if (dk <= 64 && nthr <= 256 && msm(64, nthr) <= 220 * 1024) mlstm_reg_kernel<AT, 64><<<dim3(H, E), nthr, msm(64, nthr), s>>>(HY_MLSTM_ARGS);
+    else if (dk <= 128 && nthr <= 256 && msm(128, nthr) <= 220 * 1024) mlstm_reg_kernel<AT, 128><<<dim3(H, E), nthr, msm(128, nthr), s>>>(HY_MLSTM_ARGS);
+    else mlstm_kernel<AT><<<dim3(H, E), 256, ((size_t)dk * (dv + 1) + 2 * dk + dv + 1 + 40) * 4, s>>>(HY_MLSTM_GEN_ARGS);
 #undef HY_MLSTM_ARGS
+#undef HY_MLSTM_GEN_ARGS
     h->launches++;
   }
   {

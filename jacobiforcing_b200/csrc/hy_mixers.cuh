@@ -9,6 +9,7 @@
 // Same precision rule as hy_kernels.cuh: norms, angles, decays, gates, step sizes and states are fp32 (angles fp64).
 #pragma once
 #include "hy_kernels.cuh"
+#include "jf_ptx.cuh"
 
 namespace hy {
 
@@ -515,67 +516,117 @@ glr_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_f, int
 // that column's read-out.  in [T, ld]: q, k at col_q, col_k (heads * dim each), v, g at col_v, col_g (heads * vdim);
 // gates [T, ldg] fp32: i_raw at col_i + head, f_raw at col_f + head.  state [slot][H][dim * (vdim + 1) + 1], m last.
 // Thread j keeps column j of the state in registers (key size <= DR); inputs of HY_MLSTM_TB tokens are staged by the
-// block, one thread walks the batch's gate recurrence (a scalar chain), one warp per token makes the output norm.
+// block (for long entries the next batch's raw rows travel by asynchronous copies while the current one runs), the gates' scalar
+// chain is replayed per token by 16 threads side by side, one warp per token makes the output norm.
 constexpr int HY_MLSTM_TB = 16;
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float cap_f(float z, float cap) { return cap > 0.0f ? cap * tanhf(z / cap) : z; }
 
 template <typename AT, int DR>
-__global__ void __launch_bounds__(DR > 64 ? 256 : 512)
+__global__ void __launch_bounds__(256)
 mlstm_reg_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_k, int col_v, int col_g,
                  const float* __restrict__ gates, int ldg, int col_i, int col_f, const float* __restrict__ i_bias,
                  const float* __restrict__ f_bias, const float* __restrict__ norm_w, int H, int dim, int vdim, float cap,
-                 float eps, float* __restrict__ state, AT* __restrict__ out, int ldo) {
+                 float eps, int async_ok, float* __restrict__ state, AT* __restrict__ out, int ldo) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
-  constexpr int TB = HY_MLSTM_TB;
+  constexpr int TB = HY_MLSTM_TB, CH = 16 / (int)sizeof(AT);   // elements per 16-byte copy
   const int nt = blockDim.x, nwarps = nt >> 5;
   float* sq = reinterpret_cast<float*>(hy_smem);               // [TB][DR] scaled queries
   float* sk = sq + TB * DR;                                    // [TB][DR] keys
   float* sv = sk + TB * DR;                                    // [TB][nt] values, a one in column vdim
   float* so = sv + TB * nt;                                    // [TB][nt] read-outs
-  float* sg = so + TB * nt;                                    // [5][TB]: li, lf, a, c, exp(-m); then m itself
+  float* sgt = so + TB * nt;                                   // [TB][nt] output gates sigmoid(g)
+  float* sg = sgt + TB * nt;                                   // [5][TB]: li, lf, a, c, exp(-m); then m of even / odd batches
+  float* graw = sg + 5 * TB + 4;                               // [2][2][TB] raw gate pre-activations of the batch in flight
+  AT* raw = reinterpret_cast<AT*>(graw + 4 * TB);              // [2][TB][2 DR + 2 nt] raw q | k | v | g rows in flight
+  const int rw = 2 * DR + 2 * nt;
   const int h = blockIdx.x, e = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int start = b.ent_start[e], cnt = b.ent_start[e + 1] - start, pos0 = b.ent_pos0[e];
   const int vs = vdim + 1;
   float* st = state + ((size_t)b.ent_slot[e] * H + h) * ((size_t)dim * vs + 1);
   const bool col = tid < vs;
+  // long entries: the next batch's raw rows travel to shared memory by asynchronous 16-byte copies while the current batch
+  // runs (needs rows that start and end on 16-byte boundaries); short entries (decode steps) and odd sizes stage directly
+  const bool ahead = async_ok && cnt > TB;
   float S[DR];
 #pragma unroll
   for (int i = 0; i < DR; ++i) S[i] = (col && i < dim && pos0 > 0) ? st[(size_t)i * vs + tid] : 0.0f;
   if (tid == 0) sg[5 * TB] = pos0 > 0 ? st[(size_t)dim * vs] : 0.0f;
   const float qscale = 1.0f / sqrtf((float)dim);
-  for (int j0 = 0; j0 < cnt; j0 += TB) {
-    const int nb = min(TB, cnt - j0);
-    __syncthreads();
-    for (int i = tid; i < nb * DR; i += nt) {
-      const int tt = i / DR, k = i % DR;
-      const size_t t = (size_t)(start + j0 + tt);
-      const bool ok = k < dim;
-      sq[i] = ok ? to_f(in[t * ld + col_q + h * dim + k]) * qscale : 0.0f;
-      sk[i] = ok ? to_f(in[t * ld + col_k + h * dim + k]) : 0.0f;
-    }
-    for (int i = tid; i < nb * nt; i += nt) {
-      const int tt = i / nt, k = i % nt;
-      sv[i] = k < vdim ? to_f(in[(size_t)(start + j0 + tt) * ld + col_v + h * vdim + k]) : k == vdim ? 1.0f : 0.0f;
+  const float ib = i_bias[h], fb = f_bias[h];
+  const int qc = dim / CH, vc = vdim / CH, per_tok = 2 * qc + 2 * vc;
+  auto fetch = [&](int j0, int nb, int buf) {
+    AT* dst = raw + (size_t)buf * TB * rw;
+    for (int i = tid; i < nb * per_tok; i += nt) {
+      const int tt = i / per_tok, c = i % per_tok;
+      const AT* row = in + (size_t)(start + j0 + tt) * ld;
+      const AT* src; AT* d = dst + (size_t)tt * rw;
+      if (c < qc) { src = row + col_q + h * dim + c * CH; d += c * CH; }
+      else if (c < 2 * qc) { src = row + col_k + h * dim + (c - qc) * CH; d += DR + (c - qc) * CH; }
+      else if (c < 2 * qc + vc) { src = row + col_v + h * vdim + (c - 2 * qc) * CH; d += 2 * DR + (c - 2 * qc) * CH; }
+      else { src = row + col_g + h * vdim + (c - 2 * qc - vc) * CH; d += 2 * DR + nt + (c - 2 * qc - vc) * CH; }
+      jf::cp_async_16(d, src, 16u);
     }
     if (tid < nb) {
-      const size_t t = (size_t)(start + j0 + tid);
-      sg[tid] = cap_f(gates[t * ldg + col_i + h] + i_bias[h], cap);
-      sg[TB + tid] = log_sigmoid_f(cap_f(gates[t * ldg + col_f + h] + f_bias[h], cap));
+      jf::cp_async_4(graw + (buf * 2) * TB + tid, gates + (size_t)(start + j0 + tid) * ldg + col_i + h);
+      jf::cp_async_4(graw + (buf * 2 + 1) * TB + tid, gates + (size_t)(start + j0 + tid) * ldg + col_f + h);
+    }
+    jf::cp_async_commit();
+  };
+  if (ahead) fetch(0, min(TB, cnt), 0);
+  int par = 0;
+  for (int j0 = 0; j0 < cnt; j0 += TB, par ^= 1) {
+    const int nb = min(TB, cnt - j0);
+    if (ahead) jf::cp_async_wait_all();
+    __syncthreads();
+    if (ahead) {
+      const AT* src = raw + (size_t)par * TB * rw;
+      for (int i = tid; i < nb * DR; i += nt) {
+        const int tt = i / DR, k = i % DR;
+        const bool ok = k < dim;
+        sq[i] = ok ? to_f(src[(size_t)tt * rw + k]) * qscale : 0.0f;
+        sk[i] = ok ? to_f(src[(size_t)tt * rw + DR + k]) : 0.0f;
+      }
+      for (int tt = 0; tt < nb; ++tt) {
+        sv[tt * nt + tid] = tid < vdim ? to_f(src[(size_t)tt * rw + 2 * DR + tid]) : tid == vdim ? 1.0f : 0.0f;
+        sgt[tt * nt + tid] = tid < vdim ? sigmoid_f(to_f(src[(size_t)tt * rw + 2 * DR + nt + tid])) : 0.0f;
+      }
+      if (tid < nb) {
+        sg[tid] = cap_f(graw[(par * 2) * TB + tid] + ib, cap);
+        sg[TB + tid] = log_sigmoid_f(cap_f(graw[(par * 2 + 1) * TB + tid] + fb, cap));
+      }
+    } else {
+      for (int i = tid; i < nb * DR; i += nt) {
+        const int tt = i / DR, k = i % DR;
+        const size_t t = (size_t)(start + j0 + tt);
+        const bool ok = k < dim;
+        sq[i] = ok ? to_f(in[t * ld + col_q + h * dim + k]) * qscale : 0.0f;
+        sk[i] = ok ? to_f(in[t * ld + col_k + h * dim + k]) : 0.0f;
+      }
+      for (int i = tid; i < nb * nt; i += nt) {
+        const int tt = i / nt, k = i % nt;
+        const size_t t = (size_t)(start + j0 + tt);
+        sv[i] = k < vdim ? to_f(in[t * ld + col_v + h * vdim + k]) : k == vdim ? 1.0f : 0.0f;
+        sgt[i] = k < vdim ? sigmoid_f(to_f(in[t * ld + col_g + h * vdim + k])) : 0.0f;
+      }
+      if (tid < nb) {
+        const size_t t = (size_t)(start + j0 + tid);
+        sg[tid] = cap_f(gates[t * ldg + col_i + h] + ib, cap);
+        sg[TB + tid] = log_sigmoid_f(cap_f(gates[t * ldg + col_f + h] + fb, cap));
+      }
     }
     __syncthreads();
-    if (tid == 0) {
-      float m = sg[5 * TB];
-      for (int tt = 0; tt < nb; ++tt) {
-        const float li = sg[tt], lf = sg[TB + tt];
-        const float mn = fmaxf(lf + m, li);
-        sg[2 * TB + tt] = expf(lf + m - mn);
-        sg[3 * TB + tt] = expf(li - mn);
-        sg[4 * TB + tt] = expf(-mn);
-        m = mn;
-      }
-      sg[5 * TB] = m;
+    // the running maximum is a chain of additions and maxima: thread tt replays it up to its token (the same operations in
+    // the same order as a serial walk), the exponentials of all tokens are then taken side by side
+    if (tid < nb) {
+      float m = sg[5 * TB + par], mp = m;
+      for (int r = 0; r <= tid; ++r) { mp = m; m = fmaxf(sg[TB + r] + m, sg[r]); }
+      sg[2 * TB + tid] = expf(sg[TB + tid] + mp - m);
+      sg[3 * TB + tid] = expf(sg[tid] - m);
+      sg[4 * TB + tid] = expf(-m);
+      if (tid == nb - 1) sg[5 * TB + (par ^ 1)] = m;
     }
+    if (ahead && j0 + TB < cnt) fetch(j0 + TB, min(TB, cnt - j0 - TB), par ^ 1);     // that buffer was read before the barrier above
     __syncthreads();
     for (int tt = 0; tt < nb; ++tt) {
       const float* ks = sk + tt * DR;
@@ -602,10 +653,8 @@ mlstm_reg_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_
       o2 = warp_sum(o2);
       const float inv = den / sqrtf(o2 / (float)vdim + eps);
       const size_t t = (size_t)(start + j0 + tt);
-      for (int k = lane; k < vdim; k += 32) {
-        const float gt = sigmoid_f(to_f(in[t * ld + col_g + h * vdim + k]));
-        out[t * ldo + h * vdim + k] = from_f<AT>(so[tt * nt + k] * inv * norm_w[h * vdim + k] * gt);
-      }
+      for (int k = lane; k < vdim; k += 32)
+        out[t * ldo + h * vdim + k] = from_f<AT>(so[tt * nt + k] * inv * norm_w[h * vdim + k] * sgt[tt * nt + k]);
     }
   }
   if (col) {
@@ -614,7 +663,7 @@ mlstm_reg_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_
       if (i < dim) st[(size_t)i * vs + tid] = S[i];
   }
   __syncthreads();
-  if (tid == 0) st[(size_t)dim * vs] = sg[5 * TB];
+  if (tid == 0) st[(size_t)dim * vs] = sg[5 * TB + par];
 }
 
 // The same recurrence for any head size whose state fits shared memory: S [dim][vdim + 1] in shared memory, a thread walks
