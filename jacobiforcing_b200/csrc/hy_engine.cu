@@ -1354,7 +1354,8 @@ int postnorm_layer(hy_engine* h, const Batch& b, size_t li) {
     const int ch = 16 / (int)sizeof(AT);
     const int async_ok = (dk % ch == 0 && dv % ch == 0 && h->ld_pin % ch == 0 && L.c_k % ch == 0 && L.c_v % ch == 0 && L.c_g % ch == 0) ? 1 : 0;
     auto msm = [](int dr, int nt) {
-      return (size_t)(HY_MLSTM_TB * (2 * dr + 3 * nt) + 9 * HY_MLSTM_TB + 4) * 4 + (size_t)2 * HY_MLSTM_TB * (2 * dr + 2 * nt) * sizeof(AT);
+      const size_t tb = (size_t)mlstm_tb(dr);
+      return (tb * (2 * dr + 3 * nt) + 9 * tb + 4) * 4 + 2 * tb * (2 * dr + 2 * nt) * sizeof(AT);
     };
     if (dk <= 32 && nthr <= 256 && msm(32, nthr) <= 220 * 1024) mlstm_reg_kernel<AT, 32><<<dim3(H, E), nthr, msm(32, nthr), s>>>(HY_MLSTM_ARGS);
     else if (dk <= 64 && nthr <= 256 && msm(64, nthr) <= 220 * 1024) mlstm_reg_kernel<AT, 64><<<dim3(H, E), nthr, msm(64, nthr), s>>>(HY_MLSTM_ARGS);

@@ -515,10 +515,10 @@ glr_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_f, int
 // The normaliser n is carried as one more value column whose value is always one: column vdim of the state, so n . q is
 // that column's read-out.  in [T, ld]: q, k at col_q, col_k (heads * dim each), v, g at col_v, col_g (heads * vdim);
 // gates [T, ldg] fp32: i_raw at col_i + head, f_raw at col_f + head.  state [slot][H][dim * (vdim + 1) + 1], m last.
-// Thread j keeps column j of the state in registers (key size <= DR); inputs of HY_MLSTM_TB tokens are staged by the
+// Thread j keeps column j of the state in registers (key size <= DR); inputs of 16 or 32 tokens are staged by the
 // block (for long entries the next batch's raw rows travel by asynchronous copies while the current one runs), the gates' scalar
-// chain is replayed per token by 16 threads side by side, one warp per token makes the output norm.
-constexpr int HY_MLSTM_TB = 16;
+// chain is replayed per token by one thread per token side by side, one warp per token makes the output norm.
+__host__ __device__ constexpr int mlstm_tb(int dr) { return dr > 64 ? 16 : 32; }   // tokens per staged batch of the register kernel
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float cap_f(float z, float cap) { return cap > 0.0f ? cap * tanhf(z / cap) : z; }
 
@@ -529,7 +529,7 @@ mlstm_reg_kernel(Batch b, const AT* __restrict__ in, int ld, int col_q, int col_
                  const float* __restrict__ f_bias, const float* __restrict__ norm_w, int H, int dim, int vdim, float cap,
                  float eps, int async_ok, float* __restrict__ state, AT* __restrict__ out, int ldo) {
   extern __shared__ __align__(16) unsigned char hy_smem[];
-  constexpr int TB = HY_MLSTM_TB, CH = 16 / (int)sizeof(AT);   // elements per 16-byte copy
+  constexpr int TB = mlstm_tb(DR), CH = 16 / (int)sizeof(AT);  // elements per 16-byte copy
   const int nt = blockDim.x, nwarps = nt >> 5;
   float* sq = reinterpret_cast<float*>(hy_smem);               // [TB][DR] scaled queries
   float* sk = sq + TB * DR;                                    // [TB][DR] keys

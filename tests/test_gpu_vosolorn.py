@@ -166,10 +166,11 @@ def test_marked_key_is_seen_exactly_where_the_mask_says(needle_at, how, dtype):
     assert rel_err(got, want) < tol
 
 
-@pytest.mark.parametrize("size,pool", [(1, 1), (5, 1), (3, 7), (16, 16), (17, 5), (40, 3)])
+@pytest.mark.parametrize("size,pool", [(1, 1), (5, 1), (3, 7), (16, 16), (17, 5), (40, 3), (5, 20)])
 def test_windows_and_pools_of_other_shapes(size, pool):
     """A window of one token, a pool of one (every token behind the window is its own block: full attention), a pool longer
-    than the window, both equal to the page, pools that do not divide the page (blocks straddle pages)."""
+    than the window, both equal to the page, pools that do not divide the page (blocks straddle pages), a pool longer than
+    the page."""
     cfg, w = needle_model(size=size, pool=pool, dim=16, heads=2, kv_heads=2, scale=2.0 * pool ** 0.5)
     n = 75
     for needle_at in (0, n - 1 - size, max(0, n - size - pool), n - 2):
@@ -214,6 +215,20 @@ def test_gate_cap_and_the_maximum_that_starts_at_zero(i_bias, f_bias):
         assert rel_err(oracle_logits(uncapped, w, toks), want) > 1e-3
     got, _ = run(cfg, toks, "float32", cuts=[1, 2, 30, 1], weights=w)
     assert rel_err(got, want) < TOL["float32"]
+
+
+@pytest.mark.parametrize("dim,vdim", [(16, 24), (64, 128), (128, 64), (48, 250)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_matrix_memory_long_portions(dim, vdim, dtype):
+    """Head sizes whose rows start on 16-byte boundaries and portions of several staged batches: the raw rows of the next
+    batch travel while the current one runs; a last batch that is not full; a portion that ends inside a batch."""
+    cfg = model_config([mlstm(heads=2, dim=dim, vdim=vdim, cap=8.0, mlp=None)], width=64)
+    toks = rand_tokens(150, cfg["vocab"], 33)
+    got, want = run(cfg, toks, dtype, cuts=[70, 45, 33, 1], num_pages=12)
+    assert close(got, want, dtype)
+    if dtype == "float32":
+        whole, _ = run(cfg, toks, dtype, num_pages=12)
+        assert close(whole, want)
 
 
 # ---- the first tokens, long decoding, other sizes --------------------------------------------------------------------------------
