@@ -1317,8 +1317,14 @@ int postnorm_layer(hy_engine* h, const Batch& b, size_t li) {
           tc = true;
 #define HY_WIN_ARGS b, h->units_d, cv, h->ld_cv, wc, (const bf16*)L.cache, (const bf16*)L.cache_v, (const bf16*)L.pool_k, \
           (const bf16*)L.pool_v, h->f1, h->ld_f1, cat, h->ld_cat
-          if (c.w_dim <= 64 && c.w_vdim <= 64) window_mma_kernel<64><<<h->units_n, 128, 0, s>>>(HY_WIN_ARGS);
-          else window_mma_kernel<128><<<h->units_n, 128, 0, s>>>(HY_WIN_ARGS);
+          static bool win_attr = false;
+          if (!win_attr) {
+            cudaFuncSetAttribute(window_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)window_mma_smem(64));
+            cudaFuncSetAttribute(window_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)window_mma_smem(128));
+            win_attr = true;
+          }
+          if (c.w_dim <= 64 && c.w_vdim <= 64) window_mma_kernel<64><<<h->units_n, 128, window_mma_smem(64), s>>>(HY_WIN_ARGS);
+          else window_mma_kernel<128><<<h->units_n, 128, window_mma_smem(128), s>>>(HY_WIN_ARGS);
 #undef HY_WIN_ARGS
         }
       }

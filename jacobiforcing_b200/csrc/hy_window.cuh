@@ -202,7 +202,8 @@ __global__ void __launch_bounds__(128) window_attn_kernel(Batch b, const AT* __r
 // fp32 accumulators), online softmax in fp32, O += P V with P split into a bf16 head and a bf16 remainder (the weights
 // stay 32-bit in effect).  Key and value rows are zero-padded to DP columns in shared memory (dim, vdim multiples of 8, at
 // most DP).  The output is normalised, turned back by the query's position and written as the operand of the output
-// projection: no key splits, since a row sees at most window + position / pool rows.
+// projection: no key splits, since a row sees at most window + position / pool rows.  Key / value tiles are double
+// buffered: the copies of the next tile are issued before the products of the current one.
 template <int DP>
 __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit* __restrict__ units, const bf16* __restrict__ q,
                                                          int ldq, WindowCfg c, const bf16* __restrict__ kc,
@@ -210,8 +211,9 @@ __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit
                                                          const bf16* __restrict__ vp, const float* __restrict__ vrot, int ldv,
                                                          bf16* __restrict__ out, int ldo) {
   constexpr int LD = DP + 8;                            // padded row (elements): ldmatrix rows fall into distinct banks
-  __shared__ __align__(16) bf16 ks[64 * LD];
-  __shared__ __align__(16) bf16 vs[64 * LD];            // the query tile first, value tiles afterwards
+  extern __shared__ __align__(16) unsigned char hy_smem[];
+  bf16* kbuf = reinterpret_cast<bf16*>(hy_smem);        // [2][64 * LD] key tiles: one in use, one in flight
+  bf16* vbuf = kbuf + 2 * 64 * LD;                      // [2][64 * LD] value tiles; the query tile sits in the first one at the start
   const AttnUnit u = units[blockIdx.x];
   const int R = c.H / c.G;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row < rows_total && ch < kchunks)
       v = *reinterpret_cast<const uint4*>(q + (size_t)(start + row / R) * ldq + (u.kv_head * R + row % R) * c.dim + ch * 8);
-    *reinterpret_cast<uint4*>(&vs[r * LD + ch * 8]) = v;
+    *reinterpret_cast<uint4*>(&vbuf[r * LD + ch * 8]) = v;
   }
   __syncthreads();
   uint32_t qa[DP / 16][4];
@@ -233,8 +235,9 @@ __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit
     const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
     for (int kk = 0; kk < DP / 16; ++kk)
-      jf::ldmatrix_x4(jf::smem_u32(&vs[r * LD + kk * 16 + (lane >> 4) * 8]), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+      jf::ldmatrix_x4(jf::smem_u32(&vbuf[r * LD + kk * 16 + (lane >> 4) * 8]), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
   }
+  __syncthreads();                                       // the query tile has been read: its buffer takes value tiles now
   const int r_lo = u.row0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
   const bool v_lo = r_lo < rows_total, v_hi = r_hi < rows_total;
   const int p_lo = v_lo ? pos0 + r_lo / R : -1, p_hi = v_hi ? pos0 + r_hi / R : -1;
@@ -251,11 +254,13 @@ __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit
   const int tok0 = max(0, p_first - c.window + 1) / 64 * 64;                                    // first token tile
   const int n_pool_tiles = (nb_tile + 63) / 64;
   const int n_tiles = n_pool_tiles + (p_last / 64 - tok0 / 64 + 1);
-  for (int it = 0; it < n_tiles; ++it) {
+  // copies of tile `it` into buffer it & 1 (asynchronous; rows beyond the range and columns beyond the head size are zeros)
+  auto load_tile = [&](int it) {
     const bool pooled = it < n_pool_tiles;
     const int j0 = pooled ? it * 64 : tok0 + (it - n_pool_tiles) * 64;
     const int j_end = pooled ? nb_tile : p_last + 1;
-    __syncthreads();                                     // the previous tiles (or the query tile) have been read
+    bf16* ks = kbuf + (it & 1) * 64 * LD;
+    bf16* vs = vbuf + (it & 1) * 64 * LD;
     for (int i = tid; i < 64 * (DP / 8); i += 128) {
       const int r = i / (DP / 8), ch = i % (DP / 8);
       const int j = j0 + r;
@@ -273,9 +278,17 @@ __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit
       jf::cp_async_16(&vs[r * LD + ch * 8], (pooled ? vp : vc) + rowi * c.vdim + (vok ? ch * 8 : 0), vok ? 16u : 0u);
     }
     jf::cp_async_commit();
-    jf::cp_async_wait_all();
+  };
+  load_tile(0);
+  for (int it = 0; it < n_tiles; ++it) {
+    const bool pooled = it < n_pool_tiles;
+    const int j0 = pooled ? it * 64 : tok0 + (it - n_pool_tiles) * 64;
+    const bf16* ks = kbuf + (it & 1) * 64 * LD;
+    const bf16* vs = vbuf + (it & 1) * 64 * LD;
+    if (it + 1 < n_tiles) { load_tile(it + 1); jf::cp_async_wait_1(); }       // the next tile flies under this tile's products
+    else jf::cp_async_wait_all();
     __syncthreads();
-    if (!warp_live) continue;
+    if (warp_live) {
     float s[8][4];
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f; }
@@ -358,6 +371,8 @@ __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit
         jf::mma_bf16_16816(o[np * 2 + 1], pl, b2, b3);
       }
     }
+    }
+    __syncthreads();                                     // this tile's buffer is free for the tile after the next
   }
   if (!warp_live) return;
 #pragma unroll
@@ -382,5 +397,7 @@ __global__ void __launch_bounds__(128) window_mma_kernel(Batch b, const AttnUnit
     }
   }
 }
+
+constexpr size_t window_mma_smem(int dp) { return (size_t)4 * 64 * (dp + 8) * 2; }
 
 }  // namespace hy

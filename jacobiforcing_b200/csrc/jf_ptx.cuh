@@ -129,6 +129,8 @@ __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// every group of this thread but the most recent one has landed
+__device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 // generic-proxy writes to smem that the async proxy (UMMA / bulk copies) will read need this fence
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
