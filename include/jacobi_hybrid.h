@@ -81,7 +81,7 @@ typedef struct {
    * shared expert of the same form that every token uses with weight one (0: none).  ff_act: hy_act_kind of HY_FF_GATED */
   int32_t x_route, x_plain, x_act, x_shared_ff, ff_act;
   /* HY_MIX_WINDOW (softmax attention over a sliding window plus one pooled key / value per block of w_pool tokens that
-   * lies wholly before the window): query heads, key/value heads, key size, value size, window length, block length,
+   * has its last token behind the window): query heads, key/value heads, key size, value size, window length, block length,
    * rotated dimensions of queries and keys (pairs 2i, 2i + 1; 0: none), values rotated by their own position over all
    * of w_vdim and the output turned back by the query's (0 / 1), RMS norm per head on queries and keys (0 / 1);
    * rotation base, score scale */

@@ -1,11 +1,11 @@
 // hy_window.cuh — softmax attention over a sliding window plus pooled blocks (libjf_hybrid.so).
 //
 // Position i sees the tokens j with 0 <= i - j < window and, beside them, one key and one value for every block of `pool`
-// tokens that lies wholly before the window: block b = positions [b pool, b pool + pool) is seen when
-// b pool + pool - 1 <= i - window, so i sees the blocks 0 .. floor((i - window + 1) / pool) - 1.  A block's key is the mean
-// of its keys as the cache holds them (normed and rotated), its value the mean of its cached values.  A token that has
-// left the window while its block is not yet complete behind the window is not seen at all.  Tokens and blocks share one
-// softmax.
+// tokens whose last token is already behind the window: block b = positions [b pool, b pool + pool) is seen when
+// b pool + pool - 1 <= i - window, so i sees the blocks 0 .. floor((i - window + 1) / pool) - 1.  Pooled rows:
+// K_b = (1 / pool) sum_{j in b} K_j and V_b likewise, over the rows exactly as cached (keys after norm and rotation, values
+// after their rotation).  Positions between the end of the last seen block and i - window belong to neither set.  One
+// softmax runs over the union of both sets.
 //
 //   prep     per token: RMS norm per head on queries and keys (one weight of the head's size shared by the heads), rotation
 //            of the pairs (2i, 2i + 1) of the first rot_dims dimensions by pos * f_i, values rotated by their own position

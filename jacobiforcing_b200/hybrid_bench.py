@@ -157,7 +157,7 @@ def vosolorn_description(sz: dict) -> dict:
     ffe = sz["ff"] // top
     moe = {"kind": "moe", "expert": {"ff": ffe}, "router": {"experts": 8 * top, "top": top}, "shared": {"ff": ffe}}
     dense = {"kind": "dense", "ff": sz["ff"]}
-    mem = {"heads": W // 128, "dim": 64, "vdim": 128, "gate_cap": 15.0}
+    mem = {"heads": W // 128, "dim": 64, "vdim": 128, "gate_cap": 12.0}
     att = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": 1024, "pool": 16},
            "rot": {"base": 1e6, "dims": 64}, "scale": 128 ** -0.5}
     layers = []

@@ -11,7 +11,7 @@ layer's cached latent), "hgrn2" (gated linear recurrence); routed gated experts;
 
 Architecture "Vosolorn": the sublayers read the residual stream itself and an RMS norm with a layer scale sits on each
 sublayer's output; the embedding is normed and serves as the output head.  Mixers: "attention" (softmax attention over a
-sliding window plus one pooled key / value per block of tokens that lies wholly before the window, per-head query / key
+sliding window plus one pooled key / value per block of tokens whose last token is already behind the window, per-head query / key
 norms, interleaved rotary pairs, values rotated by their own position) and "mlstm" (matrix memory with capped
 exponential gates under a running maximum); feed-forward "dense" (gated, tanh-gelu) or "moe" (plain erf-gelu experts
 chosen by the largest router logits plus a bias, softmax over the chosen, beside a shared expert).

@@ -54,7 +54,7 @@ def turn_pairs(v: torch.Tensor, positions: torch.Tensor, dims: int, base: float,
 
 # ---- attention over a window and pooled blocks ------------------------------------------------------------------------
 def visible(i: int, size: int, pool: int):
-    """What position i sees: the token positions of its window and the blocks that lie wholly before the window."""
+    """What position i sees: the token positions of its window and the blocks whose last token is already behind the window."""
     toks = [j for j in range(max(0, i - size + 1), i + 1)]
     blocks = [b for b in range((i + 1) // pool + 1) if b * pool + pool - 1 <= i - size]
     return toks, blocks

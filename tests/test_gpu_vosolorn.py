@@ -257,7 +257,7 @@ OTHER = [
     # key heads == query heads, all dimensions rotated, a value size above a warp, a key size above a warp on the matrix
     # memory, many experts of a size the tensor-core product takes
     model_config([attn(heads=4, kv_heads=4, dim=24, vdim=40, size=13, pool=2, dims=24, mlp=moe(experts=16, top=4, ff=32, shared=64)),
-                  mlstm(heads=2, dim=40, vdim=70, cap=15.0, mlp=dense(64)),
+                  mlstm(heads=2, dim=40, vdim=70, cap=10.0, mlp=dense(64)),
                   mlstm(heads=4, dim=64, vdim=31, cap=0.5, mlp=None)], width=72, vocab=130, logit_scale=0.5, eps=1e-6),
     # head sizes beyond what a thread keeps in registers (the state lives in shared memory), width not a multiple of 8,
     # value rows wider than the key rows, feed-forward sizes that are not multiples of 8

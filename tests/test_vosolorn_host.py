@@ -88,7 +88,7 @@ def test_binding_structures_follow_the_header():
 
 
 def test_mask_by_hand():
-    # window of 4, blocks of 3: position 9 sees tokens 6..9 and the blocks wholly at or before position 5: {0, 1}
+    # window of 4, blocks of 3: position 9 sees tokens 6..9 and the blocks that end at or before position 5: {0, 1}
     assert plain.visible(9, 4, 3) == ([6, 7, 8, 9], [0, 1])
     # position 8 sees tokens 5..8; block 1 = 3..5 ends at 5 > 8 - 4, so only block 0; tokens 3 and 4 are not seen at all
     assert plain.visible(8, 4, 3) == ([5, 6, 7, 8], [0])
