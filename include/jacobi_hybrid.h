@@ -4,7 +4,10 @@
  * with element-wise tanh norms and per-channel layer scales (scalar-decay state-space recurrence, attention over a shared
  * low-rank latent with a rotated key part, gated linear recurrence, routed gated experts), and blocks whose sublayers read
  * the stream itself and are RMS-normed on the way back (attention over a sliding window plus pooled blocks with rotated
- * values, matrix memory with capped exponential gates, gated dense feed-forward, routed plain experts beside a shared one).
+ * values, matrix memory with capped exponential gates, gated dense feed-forward, routed plain experts beside a shared one),
+ * and pre-norm blocks whose sublayers read the normed stream through a short convolution over time and are followed by a
+ * per-layer token input and an average over the depth (attention with capped scores, a logarithmic distance bias, a
+ * window plus kept first tokens and a sink in the denominator; clamped gated dense feed-forward; routed gated experts).
  *
  * Same conventions as jacobi_b200.h: every function returns 0 or a negative status, hy_last_error(h) gives the text,
  * plain pointers and sizes only, host buffers are caller-owned, device memory belongs to the handle, one host thread per
@@ -29,10 +32,11 @@ typedef struct hy_engine* hy_handle;
 typedef enum { HY_OK = 0, HY_ERR_INVALID = -1, HY_ERR_CUDA = -2, HY_ERR_CAPACITY = -3, HY_ERR_UNSUPPORTED = -4 } hy_status;
 typedef enum { HY_DTYPE_BF16 = 0, HY_DTYPE_F32 = 1, HY_DTYPE_F16 = 2, HY_DTYPE_I32 = 3 } hy_dtype;
 typedef enum { HY_MIX_ATTN_SCAN = 0, HY_MIX_DELTA = 1, HY_MIX_SSD = 2, HY_MIX_LATENT = 3, HY_MIX_GLR = 4, HY_MIX_WINDOW = 5,
-               HY_MIX_MLSTM = 6 } hy_mixer_kind;
+               HY_MIX_MLSTM = 6, HY_MIX_BIASED = 7 } hy_mixer_kind;
 /* HY_FF_GATED: down(act(gate x) * (up x)), act = hy_act_kind in ff_act */
 typedef enum { HY_FF_NONE = 0, HY_FF_RELU2 = 1, HY_FF_ROUTED = 2, HY_FF_GATED = 3 } hy_ff_kind;
-typedef enum { HY_ACT_SILU = 0, HY_ACT_GELU_TANH = 1, HY_ACT_GELU_ERF = 2 } hy_act_kind;
+/* HY_ACT_CLAMPED (gated pairs only): g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(1.702 g) (u + 1) */
+typedef enum { HY_ACT_SILU = 0, HY_ACT_GELU_TANH = 1, HY_ACT_GELU_ERF = 2, HY_ACT_CLAMPED = 3 } hy_act_kind;
 /* how a routed feed-forward scores its experts: sigmoid scores, group-limited choice, weights normalised to x_scale |
  * the largest logits (plus a bias per expert), weights = softmax over the chosen logits alone */
 typedef enum { HY_ROUTE_SIGMOID_GROUPS = 0, HY_ROUTE_TOP_SOFTMAX = 1 } hy_route_kind;
@@ -43,8 +47,11 @@ typedef enum { HY_NORM_RMS_OFFSET = 0, HY_NORM_TANH = 1, HY_NORM_RMS = 2 } hy_no
  * HY_BLOCK_SANDWICH: x += ls1 * n1b(mixer(n1(x))), then x += ls2 * n2b(ff(n2(x))): a norm on both sides of each sublayer
  * and a per-channel layer scale.
  * HY_BLOCK_POSTNORM: x += ls1 * n1(mixer(x)), then x += ls2 * n2(ff(x)): the sublayers read the stream itself, the norm
- * (RMS, with statistics over the width) sits on the sublayer's output. */
-typedef enum { HY_BLOCK_PARALLEL = 0, HY_BLOCK_SANDWICH = 1, HY_BLOCK_POSTNORM = 2 } hy_block_kind;
+ * (RMS, with statistics over the width) sits on the sublayer's output.
+ * HY_BLOCK_PRENORM: x += m ls1 mixer(c1(n1(x))), then x += m ls2 ff(c2(n2(x))): RMS norms with plain weights on the
+ * sublayers' inputs, c(h) = h + a causal convolution of h over time per channel (hy_model_cfg.canon_taps taps, 0: none),
+ * m = hy_model_cfg.resid_mult; then the per-layer token input and the average over the depth when the model has them. */
+typedef enum { HY_BLOCK_PARALLEL = 0, HY_BLOCK_SANDWICH = 1, HY_BLOCK_POSTNORM = 2, HY_BLOCK_PRENORM = 3 } hy_block_kind;
 typedef enum { HY_POS_SINUSOID = 0, HY_POS_NONE = 1 } hy_pos_kind;   /* what is added to the scaled embedding */
 
 typedef struct {
@@ -91,6 +98,14 @@ typedef struct {
    * c of both gate pre-activations (c tanh(z / c); <= 0: no cap) */
   int32_t t_heads, t_dim, t_vdim;
   float t_gate_cap;
+  /* HY_MIX_BIASED (softmax attention without rotation; projections with biases): query heads, key/value heads, key size,
+   * value size; position i sees j <= i with i - j < b_window (0: every j) or j < b_keep_first; b_v_mix: 1 = the values
+   * are blended with the values of the first layer that says so, v <- (1 - l) v + l v_first, l = the layer's "vmix";
+   * score = b_scale q.k, then b_softcap tanh(score / b_softcap) (<= 0: no cap), minus r1_h ln(1 + r2_h (i - j)); the
+   * softmax's denominator also holds exp(sink_h) */
+  int32_t b_heads, b_kv_heads, b_dim, b_vdim, b_window, b_keep_first, b_v_mix;
+  float b_scale, b_softcap;
+  float ff_limit;                  /* the limit of HY_ACT_CLAMPED in a HY_FF_GATED feed-forward */
 } hy_layer_cfg;
 
 typedef struct {
@@ -100,6 +115,14 @@ typedef struct {
   int32_t norm_kind, block_kind, pos_kind;   /* hy_norm_kind, hy_block_kind, hy_pos_kind */
   int32_t embed_norm;              /* 1: the embedding passes through the model's norm with the weight "embed.norm" */
   int32_t tied_head;               /* 1: the output head is the embedding table (no "head" tensor) */
+  /* HY_BLOCK_PRENORM: factor on every sublayer's result; taps of the input convolutions (0: none); size of the per-layer
+   * token input (0: none; table "side.embed" [vocab, n_layers * side_dim]); 1: each layer's result is replaced by the
+   * weighted sum of the embedding output and all layers' results so far (weights "l<i>.dwa") */
+  float resid_mult;
+  int32_t canon_taps, side_dim, depth_avg;
+  /* hashed embedding of the (previous, current) token pair, added to the scaled embedding: row (prev * pair_mul_prev +
+   * cur * pair_mul_cur) mod pair_buckets of "bigram", row pair_buckets for a request's first token (0 buckets: none) */
+  int32_t pair_buckets, pair_mul_prev, pair_mul_cur;
 } hy_model_cfg;
 
 typedef struct {

@@ -10,7 +10,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libjf_hybrid.so")
-SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "hy_attn.cuh", "hy_mixers.cuh", "hy_experts.cuh", "hy_window.cuh",
+SOURCES = [os.path.join(_HERE, "csrc", f) for f in ("hy_engine.cu", "hy_kernels.cuh", "hy_gemm.cuh", "hy_attn.cuh", "hy_mixers.cuh", "hy_experts.cuh", "hy_window.cuh", "hy_biased.cuh",
                                                         "jf_ptx.cuh")] + [
     os.path.join(ROOT, "include", "jacobi_hybrid.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
@@ -39,14 +39,18 @@ class LayerCfg(C.Structure):
                 [(n, C.c_int32) for n in ("w_heads", "w_kv_heads", "w_dim", "w_vdim", "w_window", "w_pool", "w_rot_dims",
                                           "w_rot_values", "w_qk_norm")] +
                 [("w_rot_base", C.c_float), ("w_scale", C.c_float)] +
-                [(n, C.c_int32) for n in ("t_heads", "t_dim", "t_vdim")] + [("t_gate_cap", C.c_float)])
+                [(n, C.c_int32) for n in ("t_heads", "t_dim", "t_vdim")] + [("t_gate_cap", C.c_float)] +
+                [(n, C.c_int32) for n in ("b_heads", "b_kv_heads", "b_dim", "b_vdim", "b_window", "b_keep_first", "b_v_mix")] +
+                [("b_scale", C.c_float), ("b_softcap", C.c_float), ("ff_limit", C.c_float)])
 
 
 class ModelCfg(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32),
                 ("emb_scale", C.c_float), ("logit_scale", C.c_float), ("norm_eps", C.c_float),
                 ("norm_kind", C.c_int32), ("block_kind", C.c_int32), ("pos_kind", C.c_int32),
-                ("embed_norm", C.c_int32), ("tied_head", C.c_int32)]
+                ("embed_norm", C.c_int32), ("tied_head", C.c_int32), ("resid_mult", C.c_float),
+                ("canon_taps", C.c_int32), ("side_dim", C.c_int32), ("depth_avg", C.c_int32),
+                ("pair_buckets", C.c_int32), ("pair_mul_prev", C.c_int32), ("pair_mul_cur", C.c_int32)]
 
 
 class RuntimeCfg(C.Structure):

@@ -21,6 +21,7 @@
 #include "hy_mixers.cuh"
 #include "hy_experts.cuh"
 #include "hy_window.cuh"
+#include "hy_biased.cuh"
 
 namespace hy {
 
@@ -75,6 +76,13 @@ struct LayerW {
   void* cache_v = nullptr; void* pool_k = nullptr; void* pool_v = nullptr;
   // matrix memory: gate biases, the output norm's weight (all heads), column of the gate pre-activations
   float* t_ib = nullptr; float* t_fb = nullptr; float* t_norm = nullptr; int c_i = 0;
+  // pre-norm blocks: input convolutions of both sublayers (weights; the tails live in conv_state / conv_state2), weights of
+  // the depth average, the token input's projections and norm
+  float* canon1 = nullptr; float* canon2 = nullptr; float* dwa = nullptr;
+  void* side_gate = nullptr; void* side_proj = nullptr; float* side_norm = nullptr;
+  // biased attention: bias of the merged input projection, the heads' distance-bias numbers and sinks, the blend factor
+  float* b_bias = nullptr; float* b_r1 = nullptr; float* b_r2 = nullptr; float* b_sink = nullptr; float b_lambda = 0.0f;
+  int b_mix = 0;                                  // 0: values as projected, 1: the first blending layer, 2: blends with the first
 };
 
 }  // namespace hy
@@ -90,6 +98,10 @@ struct hy_engine {
   void* embed = nullptr; void* final_norm = nullptr; void* head = nullptr; void* head_t = nullptr; double* inv_freq = nullptr;
   float* embed_norm = nullptr;
   TanhNorm final_tanh{};
+  // pre-norm blocks: hashed pair table, token-input table, the last token of each request (per state slot), normed rows,
+  // the depth average's store [layers + 1][step tokens][width], the first blending layer's values of the step
+  void* pair_table = nullptr; void* side_table = nullptr; int* prev_tok = nullptr;
+  float* hn = nullptr; float* kept = nullptr; void* vfirst = nullptr; int ld_vf = 0;
   // routed feed-forward: choices and weights per (token, choice) pair, the sorted order, the tile list
   int* x_ids = nullptr; float* x_wts = nullptr; int* x_counts = nullptr; int* x_offs = nullptr; int* x_fill = nullptr;
   int* x_tile_e = nullptr; int* x_tile_r0 = nullptr; int* x_meta = nullptr; int* x_row_tok = nullptr; int* x_pair_row = nullptr;
@@ -218,15 +230,20 @@ extern "C" int hy_create(const hy_model_cfg* model, const hy_layer_cfg* layers, 
       if (((size_t)c.t_dim * (c.t_vdim + 1) + 2 * c.t_dim + c.t_vdim + 40) * 4 > 200 * 1024 &&
           (c.t_dim > 128 || c.t_vdim > 255))
         return bad("matrix memory: the state of one head exceeds shared memory");
+    } else if (c.mixer == HY_MIX_BIASED) {
+      if (c.b_heads <= 0 || c.b_kv_heads <= 0 || c.b_heads % c.b_kv_heads) return bad("biased attention heads must be a multiple of kv_heads");
+      if (c.b_dim <= 0 || c.b_vdim <= 0 || c.b_dim > 32 * HY_ATT_MAXD || c.b_vdim > 32 * HY_ATT_MAXD) return bad("biased attention head sizes must lie in 1..640");
+      if (c.b_window < 0 || c.b_keep_first < 0) return bad("window and kept first tokens must not be negative");
     } else {
       return bad("unknown mixer kind");
     }
     const int mixer_block = (c.mixer == HY_MIX_SSD || c.mixer == HY_MIX_LATENT || c.mixer == HY_MIX_GLR) ? HY_BLOCK_SANDWICH
-                            : (c.mixer == HY_MIX_WINDOW || c.mixer == HY_MIX_MLSTM) ? HY_BLOCK_POSTNORM : HY_BLOCK_PARALLEL;
+                            : (c.mixer == HY_MIX_WINDOW || c.mixer == HY_MIX_MLSTM) ? HY_BLOCK_POSTNORM
+                            : c.mixer == HY_MIX_BIASED ? HY_BLOCK_PRENORM : HY_BLOCK_PARALLEL;
     if (mixer_block != model->block_kind) return bad("this mixer does not belong to the model's block layout");
     const bool ff_fits = c.ff_kind == HY_FF_NONE || (c.ff_kind == HY_FF_RELU2 && model->block_kind == HY_BLOCK_PARALLEL) ||
                          (c.ff_kind == HY_FF_ROUTED && model->block_kind != HY_BLOCK_PARALLEL) ||
-                         (c.ff_kind == HY_FF_GATED && model->block_kind == HY_BLOCK_POSTNORM);
+                         (c.ff_kind == HY_FF_GATED && (model->block_kind == HY_BLOCK_POSTNORM || model->block_kind == HY_BLOCK_PRENORM));
     if (!ff_fits) return bad("this feed-forward does not belong to the model's block layout");
     if (c.ff_kind == HY_FF_ROUTED) {
       if (c.x_experts <= 0 || c.x_experts > 4096 || c.x_groups <= 0 || c.x_experts % c.x_groups) return bad("experts must split into equal groups");
@@ -238,11 +255,17 @@ extern "C" int hy_create(const hy_model_cfg* model, const hy_layer_cfg* layers, 
       if (model->block_kind == HY_BLOCK_SANDWICH && (c.x_plain || c.x_shared_ff || c.x_route || c.x_act))
         return bad("norm - sublayer - norm blocks serve gated silu experts with sigmoid scores only");
       if (model->block_kind == HY_BLOCK_POSTNORM && !c.x_plain) return bad("output-normed blocks serve experts without a gate only");
+      if (model->block_kind == HY_BLOCK_PRENORM && (c.x_plain || c.x_shared_ff || c.x_route != HY_ROUTE_TOP_SOFTMAX))
+        return bad("pre-norm blocks serve gated experts chosen by the largest logits only");
     }
-    if (c.ff_kind == HY_FF_GATED && (c.ff <= 0 || c.ff_act < 0 || c.ff_act > 2)) return bad("gated feed-forward: size or activation");
+    if (c.ff_kind == HY_FF_GATED && (c.ff <= 0 || c.ff_act < 0 || c.ff_act > 3)) return bad("gated feed-forward: size or activation");
   }
-  const int want_norm = model->block_kind == HY_BLOCK_SANDWICH ? HY_NORM_TANH : model->block_kind == HY_BLOCK_POSTNORM ? HY_NORM_RMS
-                                                                                                                       : HY_NORM_RMS_OFFSET;
+  if (model->block_kind == HY_BLOCK_PRENORM) {
+    if (model->canon_taps < 0 || model->canon_taps > HY_MAX_TAPS) return bad("taps of the input convolutions must lie in 0..16");
+    if (model->side_dim < 0 || model->pair_buckets < 0) return bad("negative token-input size or pair buckets");
+  }
+  const int want_norm = model->block_kind == HY_BLOCK_SANDWICH ? HY_NORM_TANH
+                        : (model->block_kind == HY_BLOCK_POSTNORM || model->block_kind == HY_BLOCK_PRENORM) ? HY_NORM_RMS : HY_NORM_RMS_OFFSET;
   if (model->norm_kind != want_norm) return bad("block layout and norm kind do not go together");
   if (cudaSetDevice(rt->device) != cudaSuccess) return bad("cudaSetDevice failed");
   cudaStreamCreate(&h->stream);
@@ -405,6 +428,59 @@ bool tanh_norm_load(Builder& B, const std::string& name, int W, TanhNorm* n) {
   return true;
 }
 
+// Router and gated experts of a routed feed-forward ("<p>mlp.router", "<p>mlp.e<j>.gate / .up / .down"): stacked per expert
+// [gate rows | up rows] and [width, ff]; for the tensor-core product also as swizzled tiles per expert whose rows
+// alternate 16 gate features and the 16 up features that go with them.
+int load_gated_experts(hy_engine* h, Builder& B, LayerW& L, const hy_layer_cfg& c, const std::string& p, Maxima& mx) {
+  const int W = h->m.width;
+  const int E = c.x_experts, ff = c.ff;
+  if (auto t = B.get(p + "mlp.router", E, W)) { L.w_router = B.up(t->v); L.w_router_t = B.up_tiled(t->v, E, W); }
+  std::vector<float> gu, dn;
+  gu.reserve((size_t)E * 2 * ff * W);
+  dn.reserve((size_t)E * W * ff);
+  for (int e = 0; e < E && B.rc == HY_OK; ++e) {
+    const std::string x = p + "mlp.e" + std::to_string(e) + ".";
+    stack_rows(gu, B.get(x + "gate", ff, W));
+    stack_rows(gu, B.get(x + "up", ff, W));
+    stack_rows(dn, B.get(x + "down", W, ff));
+  }
+  if (B.rc != HY_OK) return B.rc;
+  L.w_gu = B.up(gu);
+  L.w_down = B.up(dn);
+  if (h->m.dtype == HY_DTYPE_BF16 && W % 8 == 0 && ff % 8 == 0) {
+    // per expert: rows [32 b, 32 b + 16) = gate features [16 b, ...), rows [32 b + 16, 32 b + 32) = the up features
+    const int fb = (ff + 15) / 16, rows = fb * 32;
+    std::vector<float> il((size_t)rows * W);
+    std::vector<uint16_t> all, one;
+    for (int e = 0; e < E; ++e) {
+      std::fill(il.begin(), il.end(), 0.0f);
+      const float* g = &gu[(size_t)e * 2 * ff * W];
+      for (int f = 0; f < ff; ++f) {
+        memcpy(&il[((size_t)(f / 16) * 32 + f % 16) * W], g + (size_t)f * W, (size_t)W * 4);
+        memcpy(&il[((size_t)(f / 16) * 32 + 16 + f % 16) * W], g + (size_t)(ff + f) * W, (size_t)W * 4);
+      }
+      pack_tiles(il.data(), rows, W, one);
+      all.insert(all.end(), one.begin(), one.end());
+      L.gu_t_stride = one.size();
+    }
+    L.gu_rows = rows;
+    if (dev_alloc(h, &L.w_gu_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+    cudaMemcpy(L.w_gu_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
+    all.clear();
+    for (int e = 0; e < E; ++e) {
+      pack_tiles(&dn[(size_t)e * W * ff], W, ff, one);
+      all.insert(all.end(), one.begin(), one.end());
+      L.down_t_stride = one.size();
+    }
+    if (dev_alloc(h, &L.w_down_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
+    cudaMemcpy(L.w_down_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
+  }
+  mx.f1 = std::max(mx.f1, E);
+  mx.in = std::max(mx.in, c.x_top * ((ff + 7) & ~7));
+  mx.f2 = std::max(mx.f2, c.x_top * W);
+  return B.rc;
+}
+
 // One layer of a norm - sublayer - norm model: its norms and layer scales, the mixer's merged input projection, the
 // mixer's small tensors, its output projection, state and cache, and the experts.
 int finalize_sandwich_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
@@ -505,51 +581,7 @@ int finalize_sandwich_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
     tanh_norm_load(B, p + "norm2", W, &L.n2);
     tanh_norm_load(B, p + "norm2b", W, &L.n2b);
     if (auto t = B.get(p + "ls2", W, -1)) L.ls2 = B.up_f32(t->v);
-    const int E = c.x_experts, ff = c.ff;
-    if (auto t = B.get(p + "mlp.router", E, W)) { L.w_router = B.up(t->v); L.w_router_t = B.up_tiled(t->v, E, W); }
-    std::vector<float> gu, dn;
-    gu.reserve((size_t)E * 2 * ff * W);
-    dn.reserve((size_t)E * W * ff);
-    for (int e = 0; e < E && B.rc == HY_OK; ++e) {
-      const std::string x = p + "mlp.e" + std::to_string(e) + ".";
-      stack_rows(gu, B.get(x + "gate", ff, W));
-      stack_rows(gu, B.get(x + "up", ff, W));
-      stack_rows(dn, B.get(x + "down", W, ff));
-    }
-    if (B.rc != HY_OK) return B.rc;
-    L.w_gu = B.up(gu);
-    L.w_down = B.up(dn);
-    if (h->m.dtype == HY_DTYPE_BF16 && W % 8 == 0 && ff % 8 == 0) {
-      // per expert: rows [32 b, 32 b + 16) = gate features [16 b, ...), rows [32 b + 16, 32 b + 32) = the up features
-      const int fb = (ff + 15) / 16, rows = fb * 32;
-      std::vector<float> il((size_t)rows * W);
-      std::vector<uint16_t> all, one;
-      for (int e = 0; e < E; ++e) {
-        std::fill(il.begin(), il.end(), 0.0f);
-        const float* g = &gu[(size_t)e * 2 * ff * W];
-        for (int f = 0; f < ff; ++f) {
-          memcpy(&il[((size_t)(f / 16) * 32 + f % 16) * W], g + (size_t)f * W, (size_t)W * 4);
-          memcpy(&il[((size_t)(f / 16) * 32 + 16 + f % 16) * W], g + (size_t)(ff + f) * W, (size_t)W * 4);
-        }
-        pack_tiles(il.data(), rows, W, one);
-        all.insert(all.end(), one.begin(), one.end());
-        L.gu_t_stride = one.size();
-      }
-      L.gu_rows = rows;
-      if (dev_alloc(h, &L.w_gu_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
-      cudaMemcpy(L.w_gu_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
-      all.clear();
-      for (int e = 0; e < E; ++e) {
-        pack_tiles(&dn[(size_t)e * W * ff], W, ff, one);
-        all.insert(all.end(), one.begin(), one.end());
-        L.down_t_stride = one.size();
-      }
-      if (dev_alloc(h, &L.w_down_t, all.size() * 2, &h->bytes_w) != HY_OK) return HY_ERR_CUDA;
-      cudaMemcpy(L.w_down_t, all.data(), all.size() * 2, cudaMemcpyHostToDevice);
-    }
-    mx.f1 = std::max(mx.f1, E);
-    mx.in = std::max(mx.in, c.x_top * ((ff + 7) & ~7));
-    mx.f2 = std::max(mx.f2, c.x_top * W);
+    if (int rc = load_gated_experts(h, B, L, c, p, mx)) return rc;
   }
   return B.rc;
 }
@@ -564,6 +596,28 @@ void interleave_gate_up(const float* gu, int ff, int W, std::vector<float>& il, 
     memcpy(&il[((size_t)(f / 16) * 32 + f % 16) * W], gu + (size_t)f * W, (size_t)W * 4);
     memcpy(&il[((size_t)(f / 16) * 32 + 16 + f % 16) * W], gu + (size_t)(ff + f) * W, (size_t)W * 4);
   }
+}
+
+// Gated dense feed-forward ("<p>mlp.gate / .up / .down"): [gate rows | up rows] stacked, and for the tensor-core product as
+// tiles whose rows alternate 16 gate and 16 up features.
+int load_gated_dense(hy_engine* h, Builder& B, LayerW& L, const hy_layer_cfg& c, const std::string& p, Maxima& mx) {
+  const int W = h->m.width, ff = c.ff;
+  std::vector<float> gu;
+  stack_rows(gu, B.get(p + "mlp.gate", ff, W));
+  stack_rows(gu, B.get(p + "mlp.up", ff, W));
+  const HostTensor* dn = B.get(p + "mlp.down", W, ff);
+  if (B.rc != HY_OK) return B.rc;
+  L.w_ff_in = B.up(gu);
+  if (h->m.dtype == HY_DTYPE_BF16 && W % 8 == 0 && ff % 8 == 0) {
+    std::vector<float> il;
+    interleave_gate_up(gu.data(), ff, W, il, &L.ff_rows);
+    L.w_ff_in_t = B.up_tiled(il, L.ff_rows, W);
+  }
+  L.w_ff_down = B.up(dn->v);
+  L.w_ff_down_t = B.up_tiled(dn->v, W, ff);
+  mx.in = std::max(mx.in, 2 * ff);
+  mx.out = std::max(mx.out, ff);
+  return B.rc;
 }
 
 void* upload_rotation(hy_engine* h, const std::vector<double>& f) {
@@ -642,24 +696,7 @@ int finalize_postnorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
   if (auto t = B.get(p + "norm2", W, -1)) L.pn2 = B.up_f32(t->v);
   if (auto t = B.get(p + "ls2", W, -1)) L.ls2 = B.up_f32(t->v);
   const int ff = c.ff;
-  if (c.ff_kind == HY_FF_GATED) {
-    std::vector<float> gu;
-    stack_rows(gu, B.get(p + "mlp.gate", ff, W));
-    stack_rows(gu, B.get(p + "mlp.up", ff, W));
-    const HostTensor* dn = B.get(p + "mlp.down", W, ff);
-    if (B.rc != HY_OK) return B.rc;
-    L.w_ff_in = B.up(gu);
-    if (h->m.dtype == HY_DTYPE_BF16 && W % 8 == 0 && ff % 8 == 0) {
-      std::vector<float> il;
-      interleave_gate_up(gu.data(), ff, W, il, &L.ff_rows);
-      L.w_ff_in_t = B.up_tiled(il, L.ff_rows, W);
-    }
-    L.w_ff_down = B.up(dn->v);
-    L.w_ff_down_t = B.up_tiled(dn->v, W, ff);
-    mx.in = std::max(mx.in, 2 * ff);
-    mx.out = std::max(mx.out, ff);
-    return B.rc;
-  }
+  if (c.ff_kind == HY_FF_GATED) return load_gated_dense(h, B, L, c, p, mx);
   const int E = c.x_experts;
   if (auto t = B.get(p + "mlp.router", E, W)) { L.w_router = B.up(t->v); L.w_router_t = B.up_tiled(t->v, E, W); }
   if (c.x_route == HY_ROUTE_TOP_SOFTMAX) { if (auto t = B.get(p + "mlp.router.b", E, -1)) L.x_rb = B.up_f32(t->v); }
@@ -705,6 +742,78 @@ int finalize_postnorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
   return B.rc;
 }
 
+// One layer of a pre-norm model: norms, layer scales, input convolutions with their tails, the biased attention's merged
+// projection with its bias, pages for keys and values, the feed-forward, the token input and the depth average's weights.
+int finalize_prenorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
+  const hy_layer_cfg& c = h->lc[i];
+  const hy_runtime_cfg& rt = h->rt;
+  LayerW& L = h->lw[i];
+  const int W = h->m.width, taps = h->m.canon_taps;
+  const std::string p = "l" + std::to_string(i) + ".", d = p + "mix.";
+  auto scalar = [&](const std::string& name, float* out) {
+    auto it = h->host.find(name);
+    if (it == h->host.end() || it->second.v.size() != 1) {
+      if (B.rc == HY_OK) B.rc = fail(h, HY_ERR_INVALID, "missing or non-scalar tensor " + name);
+      return;
+    }
+    *out = it->second.v[0];
+  };
+  if (auto t = B.get(p + "norm1", W, -1)) L.pn1 = B.up_f32(t->v);
+  if (auto t = B.get(p + "ls1", W, -1)) L.ls1 = B.up_f32(t->v);
+  if (taps > 0) {
+    if (auto t = B.get(p + "canon1", W, taps)) L.canon1 = B.up_f32(t->v);
+    if (dev_alloc(h, (void**)&L.conv_state, (size_t)rt.num_slots * (taps - 1) * W * 4, &h->bytes_state)) return HY_ERR_CUDA;
+  }
+  if (h->m.depth_avg) { if (auto t = B.get(p + "dwa", (int64_t)i + 2, -1)) L.dwa = B.up_f32(t->v); }
+  const int H = c.b_heads, G = c.b_kv_heads, D = c.b_dim, Dv = c.b_vdim;
+  const int n_in = H * D + G * D + G * Dv;
+  L.c_q = 0; L.c_k = H * D; L.c_v = H * D + G * D;
+  std::vector<float> win, bias;
+  stack_rows(win, B.get(d + "q", H * D, W));
+  stack_rows(win, B.get(d + "k", G * D, W));
+  stack_rows(win, B.get(d + "v", G * Dv, W));
+  stack_rows(bias, B.get(d + "q.b", H * D, -1));
+  stack_rows(bias, B.get(d + "k.b", G * D, -1));
+  stack_rows(bias, B.get(d + "v.b", G * Dv, -1));
+  if (auto t = B.get(d + "r1", H, -1)) L.b_r1 = B.up_f32(t->v);
+  if (auto t = B.get(d + "r2", H, -1)) L.b_r2 = B.up_f32(t->v);
+  if (auto t = B.get(d + "sink", H, -1)) L.b_sink = B.up_f32(t->v);
+  if (c.b_v_mix) {
+    L.b_mix = 1;
+    for (size_t j = 0; j < i; ++j) if (h->lc[j].b_v_mix) L.b_mix = 2;
+    if (L.b_mix == 2) scalar(d + "vmix", &L.b_lambda);
+    h->ld_vf = std::max(h->ld_vf, (G * Dv + 7) & ~7);
+  }
+  const HostTensor* wo = B.get(d + "o", W, H * Dv);
+  if (B.rc != HY_OK) return B.rc;
+  L.n_in = n_in; L.c_up = n_in;
+  L.w_in = B.up(win);
+  L.w_in_t = B.up_tiled(win, n_in, W);
+  L.b_bias = B.up_f32(bias);
+  L.k_out = H * Dv;
+  L.w_out = B.up(wo->v);
+  L.w_out_t = B.up_tiled(wo->v, W, L.k_out);
+  mx.in = std::max(mx.in, n_in); mx.out = std::max(mx.out, L.k_out); mx.f2 = std::max(mx.f2, W);
+  const size_t rows = (size_t)rt.num_pages * G * rt.page_size;
+  if (dev_alloc(h, &L.cache, rows * D * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+  if (dev_alloc(h, &L.cache_v, rows * Dv * h->esz(), &h->bytes_cache)) return HY_ERR_CUDA;
+  if (h->m.side_dim > 0) {
+    const int sd = h->m.side_dim;
+    if (auto t = B.get(p + "side.gate", sd, W)) L.side_gate = B.up(t->v);
+    if (auto t = B.get(p + "side.proj", W, sd)) L.side_proj = B.up(t->v);
+    if (auto t = B.get(p + "side.norm", W, -1)) L.side_norm = B.up_f32(t->v);
+  }
+  if (c.ff_kind == HY_FF_NONE) return B.rc;
+  if (auto t = B.get(p + "norm2", W, -1)) L.pn2 = B.up_f32(t->v);
+  if (auto t = B.get(p + "ls2", W, -1)) L.ls2 = B.up_f32(t->v);
+  if (taps > 0) {
+    if (auto t = B.get(p + "canon2", W, taps)) L.canon2 = B.up_f32(t->v);
+    if (dev_alloc(h, (void**)&L.conv_state2, (size_t)rt.num_slots * (taps - 1) * W * 4, &h->bytes_state)) return HY_ERR_CUDA;
+  }
+  if (c.ff_kind == HY_FF_GATED) return load_gated_dense(h, B, L, c, p, mx);
+  return load_gated_experts(h, B, L, c, p, mx);
+}
+
 // rows of several [n_i, k] matrices stacked
 void stack_rows(std::vector<float>& dst, const HostTensor* t) { if (t) dst.insert(dst.end(), t->v.begin(), t->v.end()); }
 
@@ -721,6 +830,10 @@ extern "C" int hy_finalize(hy_handle h) {
   if (h->m.norm_kind == HY_NORM_TANH) tanh_norm_load(B, "final.norm", W, &h->final_tanh);
   else if (auto t = B.get("final.norm", W, -1)) h->final_norm = B.up(t->v);
   if (h->m.embed_norm) { if (auto t = B.get("embed.norm", W, -1)) h->embed_norm = B.up_f32(t->v); }
+  if (h->m.block_kind == HY_BLOCK_PRENORM) {
+    if (h->m.pair_buckets > 0) { if (auto t = B.get("bigram", (int64_t)h->m.pair_buckets + 1, W)) h->pair_table = B.up(t->v); }
+    if (h->m.side_dim > 0) { if (auto t = B.get("side.embed", V, (int64_t)h->m.side_dim * h->m.n_layers)) h->side_table = B.up(t->v); }
+  }
   if (h->m.tied_head) {
     h->head = h->embed;
     if (auto t = B.get("embed", V, W)) h->head_t = B.up_tiled(t->v, V, W);
@@ -740,7 +853,8 @@ extern "C" int hy_finalize(hy_handle h) {
     const hy_layer_cfg& c = h->lc[i];
     LayerW& L = h->lw[i];
     if (h->m.block_kind != HY_BLOCK_PARALLEL) {
-      const int rc = h->m.block_kind == HY_BLOCK_SANDWICH ? finalize_sandwich_layer(h, B, i, mx) : finalize_postnorm_layer(h, B, i, mx);
+      const int rc = h->m.block_kind == HY_BLOCK_SANDWICH ? finalize_sandwich_layer(h, B, i, mx)
+                     : h->m.block_kind == HY_BLOCK_POSTNORM ? finalize_postnorm_layer(h, B, i, mx) : finalize_prenorm_layer(h, B, i, mx);
       if (rc != HY_OK) return rc;
       continue;
     }
@@ -852,6 +966,13 @@ extern "C" int hy_finalize(hy_handle h) {
   if (dev_alloc(h, &h->cv, T * h->ld_cv * es, &h->bytes_ws)) return HY_ERR_CUDA;
   if (dev_alloc(h, (void**)&h->f1, T * h->ld_f1 * 4, &h->bytes_ws)) return HY_ERR_CUDA;
   if (dev_alloc(h, (void**)&h->f2, T * h->ld_f2 * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+  if (h->m.block_kind == HY_BLOCK_PRENORM) {
+    if (dev_alloc(h, (void**)&h->hn, T * W * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+    if (h->m.depth_avg && dev_alloc(h, (void**)&h->kept, (h->lc.size() + 1) * T * W * 4, &h->bytes_ws)) return HY_ERR_CUDA;
+    if (h->ld_vf > 0 && dev_alloc(h, &h->vfirst, T * h->ld_vf * es, &h->bytes_ws)) return HY_ERR_CUDA;
+    if (dev_alloc(h, (void**)&h->prev_tok, (size_t)rt.num_slots * 4, &h->bytes_state)) return HY_ERR_CUDA;
+    HY_CUDA(cudaMemset(h->prev_tok, 0, (size_t)rt.num_slots * 4));
+  }
   const size_t mw = (size_t)rt.max_want;
   if (dev_alloc(h, &h->hw, mw * W * es, &h->bytes_ws)) return HY_ERR_CUDA;
   if (dev_alloc(h, (void**)&h->logits, mw * V * 4, &h->bytes_ws)) return HY_ERR_CUDA;
@@ -865,6 +986,7 @@ extern "C" int hy_finalize(hy_handle h) {
     for (auto& c : h->lc) {
       if (c.mixer == HY_MIX_ATTN_SCAN) { maxH = std::max(maxH, c.a_heads); maxG = std::max(maxG, c.a_kv_heads); maxD = std::max(maxD, c.a_dim); }
       if (c.mixer == HY_MIX_WINDOW) { maxH = std::max(maxH, c.w_heads); maxG = std::max(maxG, c.w_kv_heads); maxD = std::max(maxD, 8); }
+      if (c.mixer == HY_MIX_BIASED) { maxH = std::max(maxH, c.b_heads); maxG = std::max(maxG, c.b_kv_heads); maxD = std::max(maxD, 8); }
       if (c.mixer == HY_MIX_LATENT) {
         maxH = std::max(maxH, c.l_heads); maxG = std::max(maxG, 1);
         maxD = std::max(maxD, std::max(c.l_kv_rank + c.l_rot_dim, c.l_kv_rank <= 128 ? 128 : c.l_kv_rank <= 256 ? 256 : 512));
@@ -1397,7 +1519,7 @@ int postnorm_layer(hy_engine* h, const Batch& b, size_t li) {
       }
       if (!fused) {
         gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_ff_in, W, T, 2 * ff, W, to_buf(pin, h->ld_pin));
-        gated_act_kernel<AT><<<dim3((ff + 255) / 256, T), 256, 0, s>>>(pin, h->ld_pin, ff, c.ff_act, cat, h->ld_cat);
+        gated_act_kernel<AT><<<dim3((ff + 255) / 256, T), 256, 0, s>>>(pin, h->ld_pin, ff, c.ff_act, c.ff_limit, cat, h->ld_cat);
         h->launches++;
       }
     }
@@ -1487,6 +1609,213 @@ int postnorm_layer(hy_engine* h, const Batch& b, size_t li) {
   return HY_OK;
 }
 
+// Routed gated experts over the rows of hb [T, width]: router logits (fp32), the choice by the largest logits with a softmax
+// over the chosen, both products grouped by expert.  Leaves one fp32 row per (token, choice) pair in h->f2 [pairs, width];
+// returns whether the rows are in pair order (few pairs) or in the expert-sorted order (h->x_pair_row maps pairs to rows).
+template <typename AT>
+bool routed_gated_experts(hy_engine* h, int T, const AT* hb, const LayerW& L, const hy_layer_cfg& c) {
+  typedef AT WT;
+  const int W = h->m.width;
+  cudaStream_t s = h->stream;
+  AT* pin = (AT*)h->pin;
+  const int NE = c.x_experts, top = c.x_top, ff = c.ff, P = T * top, ldh = (ff + 7) & ~7;
+  const bool tc_experts = std::is_same<AT, bf16>::value && L.w_gu_t != nullptr;
+  const bool few = P <= (tc_experts ? 8 : 16);
+  {
+    ProfScope ps(h, HY_PROF_ROUTE);
+    gemm<AT, WT, float>(h, hb, W, (const WT*)L.w_router, W, T, NE, W, to_buf(h->f1, h->ld_f1), L.w_router_t);
+    route_top_kernel<<<T, 32, (size_t)NE * 4, s>>>(h->f1, h->ld_f1, nullptr, NE, top, h->x_ids, h->x_wts, few ? nullptr : h->x_counts);
+    h->launches++;
+    if (!few) {
+      route_offsets_kernel<<<1, 32, 0, s>>>(h->x_counts, NE, tc_experts ? 128 : HY_XT, h->x_offs, h->x_fill, h->x_tile_e,
+                                            h->x_tile_r0, h->x_meta);
+      route_scatter_kernel<<<(P + 255) / 256, 256, 0, s>>>(P, top, h->x_ids, h->x_offs, h->x_fill, h->x_row_tok, h->x_pair_row);
+      h->launches += 2;
+    }
+  }
+  ProfScope ps(h, HY_PROF_EXPERTS);
+  float* ys = h->f2;
+  if (few) {
+    static bool rows_attr = false;
+    if (!rows_attr) {
+      cudaFuncSetAttribute(expert_rows_kernel<AT, WT, AT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      cudaFuncSetAttribute(expert_rows_kernel<AT, WT, float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      rows_attr = true;
+    }
+    expert_rows_kernel<AT, WT, AT, true><<<dim3(std::min((ff + 7) / 8, 256), P), 256, (size_t)W * sizeof(AT), s>>>(
+        hb, W, h->x_ids, top, 1, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, pin, ldh, c.x_act);
+    expert_rows_kernel<AT, WT, float, false><<<dim3(std::min((W + 7) / 8, 256), P), 256, (size_t)ff * sizeof(AT), s>>>(
+        pin, ldh, h->x_ids, top, 0, (const WT*)L.w_down, (size_t)W * ff, W, ff, ys, W, -1);
+  } else if (tc_experts) {
+    if constexpr (std::is_same<AT, bf16>::value) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        cudaFuncSetAttribute(gemm_tc_kernel<bf16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
+        cudaFuncSetAttribute(gemm_tc_kernel<float, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(128));
+        attr_set = true;
+      }
+      const int tiles = std::min(h->x_max_tiles, P / 128 + NE + 1);
+      const TcGroup g1{h->x_meta, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_row_tok, L.gu_t_stride};
+      const TcGroup g2{h->x_meta, h->x_offs, h->x_tile_e, h->x_tile_r0, nullptr, L.down_t_stride};
+      GemmOut o1{pin, ldh, ff, nullptr, 0, 2, nullptr, 0, 1.0f};
+      o1.act_kind = c.x_act;
+      gemm_tc_kernel<bf16, 128><<<dim3((L.gu_rows + 127) / 128, tiles), 192, tc_smem_bytes(128), s>>>(
+          hb, W, (const bf16*)L.w_gu_t, P, L.gu_rows, W, o1, h->err_d, g1);
+      GemmOut o2 = to_buf(ys, W);
+      gemm_tc_kernel<float, 128><<<dim3((W + 127) / 128, tiles), 192, tc_smem_bytes(128), s>>>(
+          pin, ldh, (const bf16*)L.w_down_t, P, W, ff, o2, h->err_d, g2);
+    }
+  } else {
+    const int tiles = std::min(h->x_max_tiles, P / HY_XT + NE + 1);
+    expert_gemm_simt_kernel<AT, WT, AT, true><<<dim3((ff + 63) / 64, tiles), 256, 0, s>>>(
+        hb, W, h->x_row_tok, (const WT*)L.w_gu, (size_t)2 * ff * W, ff, W, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, pin, ldh, c.x_act);
+    expert_gemm_simt_kernel<AT, WT, float, false><<<dim3((W + 63) / 64, tiles), 256, 0, s>>>(
+        pin, ldh, nullptr, (const WT*)L.w_down, (size_t)W * ff, W, ff, h->x_offs, h->x_tile_e, h->x_tile_r0, h->x_meta, ys, W, -1);
+  }
+  h->launches += 2;
+  return few;
+}
+
+template <typename WT>
+void stream_row(hy_engine* h, const Batch& b, const StreamOp& o) {
+  const int W = h->m.width;
+  static bool attr = false;                                  // per WT: this function is a template
+  if (!attr) { cudaFuncSetAttribute(stream_row_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  stream_row_kernel<WT><<<b.T, 256, ((size_t)2 * W + (size_t)std::max(o.side_dim, 0)) * 4, h->stream>>>(b, o, W, h->x);
+  h->launches++;
+}
+
+// the normed rows in h->hn through a sublayer's input convolution into the operand buffer; then the new tail
+template <typename AT>
+void canon_input(hy_engine* h, const Batch& b, const float* w, float* tails) {
+  const int W = h->m.width, taps = h->m.canon_taps;
+  canon_kernel<AT><<<dim3((W + 127) / 128, b.T), 128, 0, h->stream>>>(b, h->hn, W, taps, w, tails, (AT*)h->hbuf);
+  h->launches++;
+  if (taps > 1) {
+    conv_tail_kernel<float><<<dim3((W + 127) / 128, b.E), 128, 0, h->stream>>>(b, h->hn, W, 0, W, taps, tails);
+    h->launches++;
+  }
+}
+
+// One layer of a pre-norm model.  On entry h->hn holds the layer's first normed rows (norm1 of the stream); on exit the
+// next layer's.  x += m ls1 attention(c1(n1 x));  x += m ls2 ff(c2(n2 x));  token input;  depth average.
+template <typename AT>
+int prenorm_layer(hy_engine* h, const Batch& b, size_t li) {
+  typedef AT WT;
+  const hy_layer_cfg& c = h->lc[li];
+  const LayerW& L = h->lw[li];
+  const int W = h->m.width, T = b.T, E = b.E;
+  const float eps = h->m.norm_eps, mult = h->m.resid_mult;
+  cudaStream_t s = h->stream;
+  AT* hb = (AT*)h->hbuf; AT* pin = (AT*)h->pin; AT* cat = (AT*)h->cat;
+  const bool last = li + 1 == h->lc.size();
+  {
+    ProfScope ps(h, HY_PROF_CONV);
+    canon_input<AT>(h, b, L.canon1, L.conv_state);
+  }
+  {
+    ProfScope ps(h, HY_PROF_GEMM_IN);
+    GemmOut o = to_buf(pin, h->ld_pin);
+    o.bias = L.b_bias;
+    gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_in, W, T, L.n_in, W, o, L.w_in_t);
+  }
+  const BiasedCfg bc{c.b_heads, c.b_kv_heads, c.b_dim, c.b_vdim, c.b_window, c.b_keep_first, c.b_scale, c.b_softcap, L.b_r1, L.b_r2, L.b_sink};
+  {
+    ProfScope ps(h, HY_PROF_CONV);
+    biased_prep_kernel<AT><<<T, 128, 0, s>>>(b, pin, h->ld_pin, L.c_k, L.c_v, c.b_kv_heads, c.b_dim, c.b_vdim, L.b_mix, L.b_lambda,
+                                             (AT*)h->vfirst, h->ld_vf, (AT*)L.cache, (AT*)L.cache_v);
+    h->launches++;
+  }
+  {
+    ProfScope ps(h, HY_PROF_ATTN);
+    bool tc = false;
+    if constexpr (std::is_same<AT, bf16>::value) {
+      static const bool simt_only = getenv("HY_BIASED_SIMT") != nullptr;      // developer switch
+      if (!simt_only && c.b_dim % 8 == 0 && c.b_vdim % 8 == 0 && c.b_dim <= 128 && c.b_vdim <= 128 && h->ld_pin % 8 == 0 && h->units_d &&
+          window_units(h, E, c.b_heads, c.b_kv_heads)) {
+        tc = true;
+        static bool attr = false;
+        if (!attr) {
+          cudaFuncSetAttribute(biased_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)window_mma_smem(64));
+          cudaFuncSetAttribute(biased_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)window_mma_smem(128));
+          attr = true;
+        }
+        if (c.b_dim <= 64 && c.b_vdim <= 64)
+          biased_mma_kernel<64><<<h->units_n, 128, window_mma_smem(64), s>>>(b, h->units_d, pin + L.c_q, h->ld_pin, bc, (const bf16*)L.cache,
+                                                                            (const bf16*)L.cache_v, cat, h->ld_cat);
+        else
+          biased_mma_kernel<128><<<h->units_n, 128, window_mma_smem(128), s>>>(b, h->units_d, pin + L.c_q, h->ld_pin, bc, (const bf16*)L.cache,
+                                                                              (const bf16*)L.cache_v, cat, h->ld_cat);
+      }
+    }
+    if (!tc)
+      biased_attn_kernel<AT, AT><<<(T * c.b_heads + 3) / 4, 128, 4 * c.b_dim * sizeof(float), s>>>(
+          b, pin + L.c_q, h->ld_pin, bc, (const AT*)L.cache, (const AT*)L.cache_v, cat, h->ld_cat);
+    h->launches++;
+  }
+  {
+    ProfScope ps(h, HY_PROF_GEMM_OUT);
+    gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_out, L.k_out, T, W, L.k_out, to_buf(h->f2, h->ld_f2), L.w_out_t);
+  }
+  // what closes the layer: the token input, the depth average and the next layer's first norm
+  StreamOp tail{};
+  tail.mult = mult; tail.eps = eps;
+  if (h->m.side_dim > 0) {
+    tail.side_gate = L.side_gate; tail.side_proj = L.side_proj; tail.side_norm = L.side_norm; tail.side_table = h->side_table;
+    tail.side_ld = h->m.side_dim * h->m.n_layers; tail.side_col0 = (int)li * h->m.side_dim; tail.side_dim = h->m.side_dim;
+  }
+  if (h->m.depth_avg) { tail.kept = h->kept; tail.kept_stride = (size_t)h->rt.max_step_tokens * W; tail.kept_n = (int)li + 1; tail.dwa = L.dwa; }
+  if (!last) { tail.next_w = h->lw[li + 1].pn1; tail.next_out = h->hn; }
+  if (c.ff_kind == HY_FF_NONE) {
+    ProfScope ps(h, HY_PROF_NORM);
+    tail.y = h->f2; tail.ldy = h->ld_f2; tail.ls = L.ls1;
+    stream_row<WT>(h, b, tail);
+    return HY_OK;
+  }
+  {
+    ProfScope ps(h, HY_PROF_NORM);
+    StreamOp o{};
+    o.y = h->f2; o.ldy = h->ld_f2; o.ls = L.ls1; o.mult = mult; o.eps = eps; o.next_w = L.pn2; o.next_out = h->hn;
+    stream_row<WT>(h, b, o);
+  }
+  {
+    ProfScope ps(h, HY_PROF_CONV);
+    canon_input<AT>(h, b, L.canon2, L.conv_state2);
+  }
+  tail.ls = L.ls2;
+  if (c.ff_kind == HY_FF_GATED) {
+    const int ff = c.ff;
+    {
+      ProfScope ps(h, HY_PROF_GEMM_IN);
+      bool fused = false;
+      if constexpr (std::is_same<AT, bf16>::value) {
+        if (T > 8 && L.w_ff_in_t && W % 8 == 0) {
+          GemmOut o{cat, h->ld_cat, ff, nullptr, 0, 2, nullptr, 0, 1.0f};
+          o.act_kind = c.ff_act; o.act_limit = c.ff_limit;
+          gemm<AT, WT, AT>(h, hb, W, (const WT*)nullptr, W, T, L.ff_rows, W, o, L.w_ff_in_t);
+          fused = true;
+        }
+      }
+      if (!fused) {
+        gemm<AT, WT, AT>(h, hb, W, (const WT*)L.w_ff_in, W, T, 2 * ff, W, to_buf(pin, h->ld_pin));
+        gated_act_kernel<AT><<<dim3((ff + 255) / 256, T), 256, 0, s>>>(pin, h->ld_pin, ff, c.ff_act, c.ff_limit, cat, h->ld_cat);
+        h->launches++;
+      }
+    }
+    {
+      ProfScope ps(h, HY_PROF_GEMM_OUT);
+      gemm<AT, WT, float>(h, cat, h->ld_cat, (const WT*)L.w_ff_down, ff, T, W, ff, to_buf(h->f2, h->ld_f2), L.w_ff_down_t);
+    }
+    tail.y = h->f2; tail.ldy = h->ld_f2;
+  } else {
+    const bool few = routed_gated_experts<AT>(h, T, hb, L, c);
+    tail.rows = h->f2; tail.ldr = W; tail.pair_row = few ? nullptr : h->x_pair_row; tail.wts = h->x_wts; tail.top = c.x_top;
+  }
+  ProfScope ps(h, HY_PROF_NORM);
+  stream_row<WT>(h, b, tail);
+  return HY_OK;
+}
+
 template <typename AT>
 int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float* layers_out) {
   typedef AT WT;
@@ -1496,7 +1825,17 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
   AT* hb = (AT*)h->hbuf; AT* pin = (AT*)h->pin; AT* cat = (AT*)h->cat; AT* cv = (AT*)h->cv;
   {
     ProfScope ps(h, HY_PROF_NORM);
-    embed_kernel<WT><<<T, 128, 0, s>>>(b, (const WT*)h->embed, h->inv_freq, h->m.emb_scale, W, h->x);
+    if (h->m.block_kind == HY_BLOCK_PRENORM) {
+      embed_pair_kernel<WT><<<T, 128, 0, s>>>(b, (const WT*)h->embed, h->m.emb_scale, (const WT*)h->pair_table, h->m.pair_buckets,
+                                              h->m.pair_mul_prev, h->m.pair_mul_cur, h->prev_tok, W, h->x, h->kept);
+      prev_token_kernel<<<(E + 127) / 128, 128, 0, s>>>(b, h->prev_tok);
+      StreamOp o{};                                            // the first layer's first norm
+      o.eps = eps; o.next_w = h->lw[0].pn1; o.next_out = h->hn;
+      stream_row<WT>(h, b, o);
+      h->launches++;
+    } else {
+      embed_kernel<WT><<<T, 128, 0, s>>>(b, (const WT*)h->embed, h->inv_freq, h->m.emb_scale, W, h->x);
+    }
     h->launches++;
     // output-normed blocks read the stream itself: it leaves here in the activation type too, normed when the model says so
     if (h->m.block_kind == HY_BLOCK_POSTNORM) post_norm_add<AT>(h, T, h->x, W, nullptr, nullptr, nullptr, 0, nullptr, h->embed_norm, nullptr, 0);
@@ -1506,7 +1845,8 @@ int run_step(hy_engine* h, const Batch& b, int n_want, const int* want_d, float*
     const LayerW& L = h->lw[li];
     if (h->m.block_kind != HY_BLOCK_PARALLEL) {
       if (h->m.block_kind == HY_BLOCK_SANDWICH) sandwich_layer<AT>(h, b, li);
-      else postnorm_layer<AT>(h, b, li);
+      else if (h->m.block_kind == HY_BLOCK_POSTNORM) postnorm_layer<AT>(h, b, li);
+      else prenorm_layer<AT>(h, b, li);
       if (layers_out) cudaMemcpyAsync(layers_out + li * (size_t)T * W, h->x, (size_t)T * W * 4, cudaMemcpyDeviceToHost, s);
       continue;
     }

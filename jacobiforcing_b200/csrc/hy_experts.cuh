@@ -88,12 +88,12 @@ __global__ void __launch_bounds__(32) route_top_kernel(const float* __restrict__
   for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= f;
 }
 
-// out[t, f] = act(in[t, f]) * in[t, n + f]: the gated pair of a dense feed-forward whose gate and up rows are stacked.
+// out[t, f] = act(in[t, f]) * in[t, n + f] (or the clamped pair, see gated_pair_f): the gated pair of a dense feed-forward whose gate and up rows are stacked.
 template <typename AT>
-__global__ void gated_act_kernel(const AT* __restrict__ in, int ldi, int n, int act, AT* __restrict__ out, int ldo) {
+__global__ void gated_act_kernel(const AT* __restrict__ in, int ldi, int n, int act, float limit, AT* __restrict__ out, int ldo) {
   const int t = blockIdx.y;
   const int f = blockIdx.x * blockDim.x + threadIdx.x;
-  if (f < n) out[(size_t)t * ldo + f] = from_f<AT>(act_f(act, to_f(in[(size_t)t * ldi + f])) * to_f(in[(size_t)t * ldi + n + f]));
+  if (f < n) out[(size_t)t * ldo + f] = from_f<AT>(gated_pair_f(act, to_f(in[(size_t)t * ldi + f]), to_f(in[(size_t)t * ldi + n + f]), limit));
 }
 
 // Tiles of tile_rows rows of one expert (HY_XT for the SIMT product, 128 for the tensor-core product).  meta: [0] number

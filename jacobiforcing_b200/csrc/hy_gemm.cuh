@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const bf16* __restrict__ X
             const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
             const int f = ((n0 + warp * 32) >> 1) + lane;
             if (lane < 16 && f < o.split && t0 + c0 + j < T)
-              ((TO*)o.out1)[(size_t)(t0 + c0 + j) * o.ld1 + f] = from_f<TO>(act_f(o.act_kind, mine) * other);
+              ((TO*)o.out1)[(size_t)(t0 + c0 + j) * o.ld1 + f] = from_f<TO>(gated_pair_f(o.act_kind, mine, other, o.act_limit));
           }
           continue;
         }

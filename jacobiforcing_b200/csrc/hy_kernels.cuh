@@ -29,6 +29,16 @@ __device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.0f 
 __device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
 // activation by kind: 0 silu, 1 the tanh form of gelu, 2 gelu with the error function
 __device__ __forceinline__ float act_f(int kind, float z) { return kind == 1 ? gelu_tanh_f(z) : kind == 2 ? gelu_erf_f(z) : silu_f(z); }
+// a gated pair by kind: act(gate) * up, or (kind 3) the clamped pair g = min(gate, limit), u = clamp(up, -limit, limit),
+// g sigmoid(1.702 g) (u + 1)
+__device__ __forceinline__ float gated_pair_f(int kind, float g, float u, float limit) {
+  if (kind == 3) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoid_f(1.702f * g) * (u + 1.0f);
+  }
+  return act_f(kind, g) * u;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -126,17 +136,21 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // (tanh(next_alpha x) next_w[n] + next_b[n]) into next_out [T, ldr] in the activation type: no separate norm launch.
 // act2 == 3: every column passes through the activation act_kind (act_f) before it is stored.  out2_f32: the columns from
 // `split` on leave as fp32 whatever the output type (gate pre-activations of a recurrence beside its bf16 operands).
+// bias: added to the scaled accumulator of column n before anything else (projections with biases).  act_limit: the limit
+// of the clamped gated pair (act2 == 2 with act_kind 3).
 struct GemmOut {
   void* out1; int ld1; int split; void* out2; int ld2; int act2;
   float* resid; int ldr; float alpha;
   const float* post_w; const float* post_b; const float* post_ls; float post_alpha;
   const float* next_w; const float* next_b; float next_alpha; void* next_out; int next_f32;
   int act_kind; int out2_f32;
+  const float* bias; float act_limit;
 };
 
 template <typename TO>
 __device__ __forceinline__ void gemm_store(const GemmOut& o, int t, int n, float c) {
   c *= o.alpha;
+  if (o.bias) c += o.bias[n];
   if (o.resid) {
     if (o.post_w) c = o.post_ls[n] * fmaf(tanhf(o.post_alpha * c), o.post_w[n], o.post_b[n]);
     const float v = o.resid[(size_t)t * o.ldr + n] + c;

@@ -16,6 +16,15 @@ norms, interleaved rotary pairs, values rotated by their own position) and "mlst
 exponential gates under a running maximum); feed-forward "dense" (gated, tanh-gelu) or "moe" (plain erf-gelu experts
 chosen by the largest router logits plus a bias, softmax over the chosen, beside a shared expert).
 
+Architecture "Sebavik": pre-norm blocks whose sublayers read the RMS-normed stream through a short causal convolution over
+time (h + conv(h)) and whose results are scaled per channel and by one factor of the model; a per-layer token input (a
+slice of a second embedding table, gated by the stream) and a weighted average over the depth close every layer.  Mixer
+"attention": no rotation; scores scaled, capped by a tanh and lowered by a logarithmic distance bias; a sliding window
+plus the sequence's first tokens; a per-head sink in the softmax's denominator; biased projections; values blended with
+those of the first such layer.  Feed-forward "dense" (clamped gated pair) or "moe" (gated silu experts chosen by the
+largest router logits, softmax over the chosen).  The scaled embedding gets a hashed embedding of the (previous, current)
+token pair added and serves as the output head.
+
 Every size and every constant that can differ between models is read from config.json; sizes that only the tensors know
 (the inner sizes of the two-step decay and gate projections) are read from the checkpoint's tensor shapes."""
 from __future__ import annotations
@@ -28,12 +37,12 @@ from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 
-MIX_ATTN_SCAN, MIX_DELTA, MIX_SSD, MIX_LATENT, MIX_GLR, MIX_WINDOW, MIX_MLSTM = 0, 1, 2, 3, 4, 5, 6
+MIX_ATTN_SCAN, MIX_DELTA, MIX_SSD, MIX_LATENT, MIX_GLR, MIX_WINDOW, MIX_MLSTM, MIX_BIASED = 0, 1, 2, 3, 4, 5, 6, 7
 FF_NONE, FF_RELU2, FF_ROUTED, FF_GATED = 0, 1, 2, 3
-ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_CLAMPED = 0, 1, 2, 3
 ROUTE_SIGMOID_GROUPS, ROUTE_TOP_SOFTMAX = 0, 1
 NORM_RMS_OFFSET, NORM_TANH, NORM_RMS = 0, 1, 2
-BLOCK_PARALLEL, BLOCK_SANDWICH, BLOCK_POSTNORM = 0, 1, 2
+BLOCK_PARALLEL, BLOCK_SANDWICH, BLOCK_POSTNORM, BLOCK_PRENORM = 0, 1, 2, 3
 POS_SINUSOID, POS_NONE = 0, 1
 _ST_DTYPES = {"BF16": (0, 2), "F32": (1, 4), "F16": (2, 2), "I32": (3, 4)}
 
@@ -120,6 +129,17 @@ class LayerSpec:
     t_dim: int = 0
     t_vdim: int = 0
     t_gate_cap: float = 0.0
+    # attention with capped scores, a distance bias, a window plus kept first tokens and a sink
+    b_heads: int = 0
+    b_kv_heads: int = 0
+    b_dim: int = 0
+    b_vdim: int = 0
+    b_window: int = 0
+    b_keep_first: int = 0
+    b_v_mix: int = 0
+    b_scale: float = 1.0
+    b_softcap: float = 0.0
+    ff_limit: float = 0.0
 
     def cache_elems_per_token(self) -> int:
         """Elements this layer keeps in the paged cache for every token of a request."""
@@ -129,6 +149,8 @@ class LayerSpec:
             return self.l_kv_rank + self.l_rot_dim
         if self.mixer == MIX_WINDOW:                  # keys and values, and their pooled blocks
             return -(-self.w_kv_heads * (self.w_dim + self.w_vdim) * (self.w_pool + 1) // self.w_pool)
+        if self.mixer == MIX_BIASED:
+            return self.b_kv_heads * (self.b_dim + self.b_vdim)
         return 0
 
 
@@ -202,6 +224,29 @@ def _plain_experts_ff(spec: LayerSpec, mlp: dict) -> None:
         raise ValueError("mixture of experts: top must lie in 1..experts")
 
 
+def _biased_spec(m: dict) -> LayerSpec:
+    mask = m.get("mask") or {}
+    spec = LayerSpec(MIX_BIASED, b_heads=int(m["heads"]), b_kv_heads=int(m["kv_heads"]), b_dim=int(m["dim"]),
+                     b_vdim=int(m["vdim"]), b_window=int(mask.get("size") or 0), b_keep_first=int(mask.get("keep_first") or 0),
+                     b_v_mix=1 if m.get("v_mix") else 0, b_scale=float(m["scale"]), b_softcap=float(m.get("softcap") or 0.0))
+    if spec.b_heads <= 0 or spec.b_kv_heads <= 0 or spec.b_heads % spec.b_kv_heads:
+        raise ValueError("attention: heads must be a positive multiple of kv_heads")
+    if spec.b_dim <= 0 or spec.b_vdim <= 0:
+        raise ValueError("attention: dim and vdim must be positive")
+    if spec.b_window < 0 or spec.b_keep_first < 0:
+        raise ValueError("attention: mask.size and mask.keep_first must not be negative")
+    return spec
+
+
+def _gated_experts_ff(spec: LayerSpec, mlp: dict) -> None:
+    r = mlp["router"]
+    spec.ff_kind, spec.ff = FF_ROUTED, int(mlp["expert"]["ff"])
+    spec.x_experts, spec.x_top = int(r["experts"]), int(r["top"])
+    spec.x_route, spec.x_plain, spec.x_act = ROUTE_TOP_SOFTMAX, 0, ACT_SILU
+    if not 1 <= spec.x_top <= spec.x_experts:
+        raise ValueError("mixture of experts: top must lie in 1..experts")
+
+
 @dataclass
 class HybridConfig:
     architecture: str
@@ -216,6 +261,13 @@ class HybridConfig:
     pos_kind: int = POS_SINUSOID
     embed_norm: bool = False
     tied_head: bool = False
+    resid_mult: float = 1.0
+    canon_taps: int = 0
+    side_dim: int = 0
+    depth_avg: int = 0
+    pair_buckets: int = 0
+    pair_mul_prev: int = 0
+    pair_mul_cur: int = 0
     # what the engine's configuration reads from a model description
     max_position_embeddings: int = 1 << 30          # positions enter through a sinusoid or a rotation: no table to run out of
     is_hybrid: bool = True
@@ -231,6 +283,8 @@ class HybridConfig:
             return cls._famepel(cfg)
         if cfg.get("architecture") == "Vosolorn":
             return cls._vosolorn(cfg)
+        if cfg.get("architecture") == "Sebavik":
+            return cls._sebavik(cfg)
         layers = []
         for i, lc in enumerate(cfg["layers"]):
             m = lc["mixer"]
@@ -308,6 +362,39 @@ class HybridConfig:
         return cls(architecture="Vosolorn", width=int(cfg["width"]), vocab=int(cfg["vocab"]), emb_scale=1.0,
                    logit_scale=float(cfg.get("logit_scale", 1.0)), norm_eps=float(cfg["norm"]["eps"]), layers=layers,
                    norm_kind=NORM_RMS, block_kind=BLOCK_POSTNORM, pos_kind=POS_NONE, embed_norm=True, tied_head=True)
+
+    @classmethod
+    def _sebavik(cls, cfg: dict) -> "HybridConfig":
+        layers: List[LayerSpec] = []
+        mixes = []
+        for i, lc in enumerate(cfg["layers"]):
+            if lc["type"] != "attention":
+                raise NotImplementedError(f"layer type {lc['type']!r}")
+            spec = _biased_spec(lc["mixer"])
+            if spec.b_v_mix:
+                mixes.append(spec)
+                if (spec.b_kv_heads, spec.b_vdim) != (mixes[0].b_kv_heads, mixes[0].b_vdim):
+                    raise ValueError(f"layer {i}: blended values need the kv_heads and vdim of the first blending layer")
+            mlp = lc.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") == "dense":
+                    spec.ff_kind, spec.ff, spec.ff_act, spec.ff_limit = FF_GATED, int(mlp["ff"]), ACT_CLAMPED, float(mlp["limit"])
+                elif mlp.get("kind") == "moe":
+                    _gated_experts_ff(spec, mlp)
+                else:
+                    raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
+            layers.append(spec)
+        emb = cfg["embedding"]
+        pair = emb.get("bigram") or {}
+        taps = int((cfg.get("canon") or {}).get("taps", 0))
+        if not 0 <= taps <= 16:
+            raise ValueError("canon.taps must lie in 0..16")
+        return cls(architecture="Sebavik", width=int(cfg["width"]), vocab=int(cfg["vocab"]), emb_scale=float(emb.get("scale", 1.0)),
+                   logit_scale=1.0, norm_eps=float(cfg["norm"]["eps"]), layers=layers, norm_kind=NORM_RMS,
+                   block_kind=BLOCK_PRENORM, pos_kind=POS_NONE, tied_head=True, resid_mult=float(cfg.get("residual_mult", 1.0)),
+                   canon_taps=taps, side_dim=int((cfg.get("token_side") or {}).get("dim", 0)), depth_avg=1,
+                   pair_buckets=int(pair.get("buckets", 0)), pair_mul_prev=int(pair.get("mul_prev", 0)),
+                   pair_mul_cur=int(pair.get("mul_cur", 0)))
 
     @classmethod
     def from_dir(cls, path: str) -> "HybridConfig":

@@ -40,7 +40,8 @@ class HybridRuntime:
         self.max_want = max_want or max_step_tokens
         m = cabi.ModelCfg(config.width, config.vocab, len(config.layers), DTYPES[dtype], config.emb_scale,
                           config.logit_scale, config.norm_eps, config.norm_kind, config.block_kind, config.pos_kind,
-                          int(config.embed_norm), int(config.tied_head))
+                          int(config.embed_norm), int(config.tied_head), config.resid_mult, config.canon_taps,
+                          config.side_dim, config.depth_avg, config.pair_buckets, config.pair_mul_prev, config.pair_mul_cur)
         layers = (cabi.LayerCfg * len(config.layers))()
         for i, s in enumerate(config.layers):
             for name, _ in cabi.LayerCfg._fields_:

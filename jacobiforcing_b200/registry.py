@@ -41,6 +41,7 @@ FAMILIES: Dict[str, ModelFamily] = {
     "Kinetar": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
     "Famepel": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
     "Vosolorn": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
+    "Sebavik": ModelFamily("hybrid", True, _hybrid_config, _hybrid_runner),
 }
 
 
