@@ -90,14 +90,14 @@ def attention(h: torch.Tensor, p: Dict[str, torch.Tensor], c: dict, v: torch.Ten
         dist = torch.tensor([i - j for j in js], dtype=h.dtype)
         for hh in range(H):
             g = hh // (H // G)
-            s = torch.stack([q[i, hh] @ k[j, g] for j in js]) * float(c["scale"])
+            s = (k[js, g] @ q[i, hh]) * float(c["scale"])
             if cap:
                 s = float(cap) * torch.tanh(s / float(cap))
             s = s - p["r1"][hh] * torch.log1p(p["r2"][hh] * dist)
             top = torch.maximum(s.max(), p["sink"][hh])
             w = torch.exp(s - top)
             w = w / (w.sum() + torch.exp(p["sink"][hh] - top))             # the sink: one more term below, nothing above
-            out[i, hh] = sum(w[n] * v[j, g] for n, j in enumerate(js))
+            out[i, hh] = w @ v[js, g]
     return out.reshape(T, H * Dv) @ p["o"].T
 
 
@@ -176,3 +176,80 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         if layers_out is not None:
             layers_out.append(x.clone())
     return (unit_rms(x, eps) * weights["final.norm"].to(dtype)) @ weights["embed"].to(dtype).T
+
+
+# ---- tensors of a configuration, random weights -----------------------------------------------------------------------------------
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    W, V, L = int(cfg["width"]), int(cfg["vocab"]), len(cfg["layers"])
+    taps = int((cfg.get("canon") or {}).get("taps", 0))
+    side = int((cfg.get("token_side") or {}).get("dim", 0))
+    out = {"embed": (V, W), "final.norm": (W,)}
+    pair = cfg["embedding"].get("bigram")
+    if pair:
+        out["bigram"] = (int(pair["buckets"]) + 1, W)
+    if side:
+        out["side.embed"] = (V, side * L)
+    for i, lc in enumerate(cfg["layers"]):
+        p, c = f"l{i}.", lc["mixer"]
+        H, G, D, Dv = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
+        out.update({p + "norm1": (W,), p + "ls1": (W,), p + "dwa": (i + 2,),
+                    p + "mix.q": (H * D, W), p + "mix.q.b": (H * D,), p + "mix.k": (G * D, W), p + "mix.k.b": (G * D,),
+                    p + "mix.v": (G * Dv, W), p + "mix.v.b": (G * Dv,), p + "mix.vmix": (), p + "mix.r1": (H,), p + "mix.r2": (H,),
+                    p + "mix.sink": (H,), p + "mix.o": (W, H * Dv)})
+        if taps:
+            out[p + "canon1"] = (W, taps)
+        if side:
+            out.update({p + "side.gate": (side, W), p + "side.proj": (W, side), p + "side.norm": (W,)})
+        mlp = lc.get("mlp")
+        if mlp is None:
+            continue
+        out.update({p + "norm2": (W,), p + "ls2": (W,)})
+        if taps:
+            out[p + "canon2"] = (W, taps)
+        if mlp["kind"] == "dense":
+            out.update({p + "mlp.gate": (mlp["ff"], W), p + "mlp.up": (mlp["ff"], W), p + "mlp.down": (W, mlp["ff"])})
+        else:
+            ff = mlp["expert"]["ff"]
+            out[p + "mlp.router"] = (mlp["router"]["experts"], W)
+            for e in range(mlp["router"]["experts"]):
+                out.update({p + f"mlp.e{e}.gate": (ff, W), p + f"mlp.e{e}.up": (ff, W), p + f"mlp.e{e}.down": (W, ff)})
+    return out
+
+
+def random_weights(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random bf16 weights: matrices ~ N(0, 1 / in) (queries and keys twice that, so that the cap, the bias and the mask
+    matter), norm weights and layer scales near one, distance-bias numbers and blend factors inside (0, 1), depth weights
+    that favour the layer's own result."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        leaf = name.split(".", 1)[1] if name.startswith("l") and name[1].isdigit() else name
+        if leaf in ("embed", "side.embed"):
+            t = torch.randn(shape, generator=g)
+        elif leaf == "bigram":
+            t = torch.randn(shape, generator=g) * 0.5
+        elif leaf in ("canon1", "canon2"):
+            t = torch.randn(shape, generator=g) * 0.3
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) / math.sqrt(shape[1])
+            if leaf in ("mix.q", "mix.k"):
+                t = t * 2.0
+        elif leaf in ("mix.q.b", "mix.k.b", "mix.v.b"):
+            t = torch.randn(shape, generator=g) * 0.3
+        elif leaf == "mix.r1":
+            t = 0.2 + 0.8 * torch.rand(shape, generator=g)
+        elif leaf == "mix.r2":
+            t = 0.05 + 0.45 * torch.rand(shape, generator=g)
+        elif leaf == "mix.sink":
+            t = torch.randn(shape, generator=g)
+        elif leaf == "mix.vmix":
+            t = 0.2 + 0.6 * torch.rand(shape, generator=g)
+        elif leaf == "dwa":
+            t = torch.randn(shape, generator=g) * 0.25
+            t[-1] += 1.0
+        elif leaf in ("ls1", "ls2"):
+            t = 0.5 + torch.rand(shape, generator=g)
+        else:
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        out[name] = t.to(torch.bfloat16)
+    return out
