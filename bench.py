@@ -532,6 +532,34 @@ def run_compare_vosolorn(args):
                       "peaks": peaks, "clocks": clocks, "results": res}))
 
 
+def run_compare_sebavik(args):
+    """Option --compare-sebavik: Sebavik (pre-norm blocks with input convolutions, biased attention over a window plus kept
+    first tokens, clamped gated dense feed-forward and gated experts) beside the closest existing model, Vosolorn with
+    attention in every layer, at equal width, depth, heads and feed-forward size; device times from CUDA events, three
+    warm-up passes, weights + activations larger than L2."""
+    import __graft_entry__ as g
+    g.build()
+    from jacobiforcing_b200 import hybrid_bench as hb
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        peaks = {"hbm_gbs": float(mp["hbm_gbs"]), "bf16_tflops": float(mp["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    mon = ClockSampler(0)
+    mon.start()
+    res = []
+    for size in args.compare_sebavik.split(","):
+        row = {"size": size}
+        row["sebavik"] = hb.run_hybrid(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks, design="Sebavik")
+        row["vosolorn_attention"] = hb.run_hybrid(size, args.hybrid_prompt, args.hybrid_decode_steps, [1, 8], peaks,
+                                                  design="VosolornAttention")
+        res.append(row)
+    clocks = mon.stop()
+    print(json.dumps({"metric": "sebavik_vs_vosolorn_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "peaks": peaks, "clocks": clocks, "results": res}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -565,6 +593,9 @@ def main():
     ap.add_argument("--compare-vosolorn", default="", metavar="SIZES",
                     help="instead of the headline workload: prefill / decode throughput of Vosolorn beside Famepel at equal "
                          "size, e.g. w1024,w2048 (one JSON line)")
+    ap.add_argument("--compare-sebavik", default="", metavar="SIZES",
+                    help="instead of the headline workload: prefill / decode throughput of Sebavik beside Vosolorn (attention "
+                         "in every layer) at equal size, e.g. w1024,w2048 (one JSON line)")
     ap.add_argument("--hybrid-prompt", type=int, default=4096)
     ap.add_argument("--hybrid-decode-steps", type=int, default=35)
     args = ap.parse_args()
@@ -576,6 +607,9 @@ def main():
         return
     if args.compare_vosolorn:
         run_compare_vosolorn(args)
+        return
+    if args.compare_sebavik:
+        run_compare_sebavik(args)
         return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3                                  # timing rule: at least three warm-up steps

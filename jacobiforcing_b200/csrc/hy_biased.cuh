@@ -65,7 +65,7 @@ struct StreamOp {
   const float* y; int ldy;                                   // a sublayer's rows [T, ldy], or
   const float* rows; int ldr; const int* pair_row; const float* wts; int top;   // the mixture sum_k wts[t, k] rows[pair_row[t top + k]]
   const float* ls; float mult;                               // x += mult * ls * y  (ls NULL: one; y and rows NULL: nothing added)
-  const void* side_gate; const void* side_proj; const float* side_norm; const void* side_table;
+  const void* side_gate; const void* side_proj; const float* side_norm; const void* side_table;   // side_proj: [side_dim, width]
   int side_ld, side_col0, side_dim;                          // token input: table row slice [side_col0, + side_dim)
   float* kept; size_t kept_stride; int kept_n; const float* dwa;   // kept[kept_n] <- x;  x <- sum_{j <= kept_n} dwa[j] kept[j]
   const float* next_w; float* next_out;                      // next_out[t] <- x / rms(x) * next_w  (fp32)
@@ -99,22 +99,65 @@ __global__ void __launch_bounds__(256) stream_row_kernel(Batch b, StreamOp o, in
   }
   __syncthreads();
   if (o.side_dim > 0) {
-    const WT* gate = (const WT*)o.side_gate;
-    const WT* proj = (const WT*)o.side_proj;
+    const WT* gate = (const WT*)o.side_gate;                 // [side_dim, width]
+    const WT* projT = (const WT*)o.side_proj;                // [side_dim, width]: the projection, transposed
     const WT* erow = (const WT*)o.side_table + (size_t)b.tok[t] * o.side_ld + o.side_col0;
-    for (int d = warp; d < o.side_dim; d += nw) {
-      float dot = 0.0f;
-      for (int c = lane; c < width; c += 32) dot = fmaf(xs[c], to_f(gate[(size_t)d * width + c]), dot);
-      dot = warp_sum(dot);
-      if (lane == 0) gs[d] = gelu_tanh_f(dot) * to_f(erow[d]);
+    constexpr int VEC = 16 / (int)sizeof(WT);
+    if (width % VEC == 0) {
+      // a warp owns up to four gate rows at a time; every chunk of the row read from shared memory serves all four
+      for (int base = 0; base < o.side_dim; base += nw * 4) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int c = lane * VEC; c < width; c += 32 * VEC) {
+          float xv[VEC];
+#pragma unroll
+          for (int j = 0; j < VEC; j += 4) *reinterpret_cast<float4*>(&xv[j]) = *reinterpret_cast<const float4*>(&xs[c + j]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int d = base + warp + nw * i;
+            if (d < o.side_dim) {
+              const VecN<WT, VEC> gv = *reinterpret_cast<const VecN<WT, VEC>*>(gate + (size_t)d * width + c);
+#pragma unroll
+              for (int j = 0; j < VEC; ++j) acc[i] = fmaf(xv[j], to_f(gv.v[j]), acc[i]);
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int d = base + warp + nw * i;
+          const float dot = warp_sum(acc[i]);
+          if (lane == 0 && d < o.side_dim) gs[d] = gelu_tanh_f(dot) * to_f(erow[d]);
+        }
+      }
+    } else {
+      for (int d = warp; d < o.side_dim; d += nw) {
+        float dot = 0.0f;
+        for (int c = lane; c < width; c += 32) dot = fmaf(xs[c], to_f(gate[(size_t)d * width + c]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) gs[d] = gelu_tanh_f(dot) * to_f(erow[d]);
+      }
     }
     __syncthreads();
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      float y = 0.0f;
-      for (int d = 0; d < o.side_dim; ++d) y = fmaf(to_f(proj[(size_t)c * o.side_dim + d]), gs[d], y);
-      ys[c] = y;
-      ss = fmaf(y, y, ss);
+    if (width % 4 == 0) {
+      for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+        float y[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int d = 0; d < o.side_dim; ++d) {
+          const VecN<WT, 4> pv = *reinterpret_cast<const VecN<WT, 4>*>(projT + (size_t)d * width + c);
+          const float g = gs[d];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) y[j] = fmaf(to_f(pv.v[j]), g, y[j]);
+        }
+        *reinterpret_cast<float4*>(&ys[c]) = make_float4(y[0], y[1], y[2], y[3]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss = fmaf(y[j], y[j], ss);
+      }
+    } else {
+      for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float y = 0.0f;
+        for (int d = 0; d < o.side_dim; ++d) y = fmaf(to_f(projT[(size_t)d * width + c]), gs[d], y);
+        ys[c] = y;
+        ss = fmaf(y, y, ss);
+      }
     }
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)width + o.eps);
@@ -144,27 +187,29 @@ __global__ void __launch_bounds__(256) stream_row_kernel(Batch b, StreamOp o, in
 // ---- a sublayer's input: the normed row plus its causal convolution over time ------------------------------------------------------
 // hn [T, width] fp32 normed rows; w [width, taps] fp32 (last tap = the current token); state [slot][taps - 1][width] fp32 =
 // the request's last taps - 1 normed rows.  taps == 0: the normed row passes as it is.
-template <typename AT>
+template <typename AT, int CH>
 __global__ void canon_kernel(Batch b, const float* __restrict__ hn, int width, int taps, const float* __restrict__ w,
                              const float* __restrict__ state, AT* __restrict__ out) {
   const int t = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * CH;         // CH consecutive channels per thread (width % CH == 0)
   if (c >= width) return;
-  float acc = hn[(size_t)t * width + c];
+  float acc[CH];
+#pragma unroll
+  for (int k = 0; k < CH; ++k) acc[k] = hn[(size_t)t * width + c + k];
   if (taps > 0) {
     const int e = b.tok_ent[t];
     const int start = b.ent_start[e], pos0 = b.ent_pos0[e], j = t - start;
     const float* st = state + (size_t)b.ent_slot[e] * (taps - 1) * width;
     for (int i = 0; i < taps; ++i) {
       const int src = j - (taps - 1) + i;
-      float v;
-      if (src >= 0) v = hn[(size_t)(start + src) * width + c];
-      else if (pos0 + src >= 0) v = st[(size_t)(taps - 1 + src) * width + c];
-      else v = 0.0f;
-      acc = fmaf(w[(size_t)c * taps + i], v, acc);
+      const float* row = src >= 0 ? hn + (size_t)(start + src) * width : pos0 + src >= 0 ? st + (size_t)(taps - 1 + src) * width : nullptr;
+      if (!row) continue;
+#pragma unroll
+      for (int k = 0; k < CH; ++k) acc[k] = fmaf(w[(size_t)(c + k) * taps + i], row[c + k], acc[k]);
     }
   }
-  out[(size_t)t * width + c] = from_f<AT>(acc);
+#pragma unroll
+  for (int k = 0; k < CH; ++k) out[(size_t)t * width + c + k] = from_f<AT>(acc[k]);
 }
 
 // ---- values blended with the first blending layer's; keys and values into their pages ----------------------------------------------

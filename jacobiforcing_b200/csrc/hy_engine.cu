@@ -800,7 +800,12 @@ int finalize_prenorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
   if (h->m.side_dim > 0) {
     const int sd = h->m.side_dim;
     if (auto t = B.get(p + "side.gate", sd, W)) L.side_gate = B.up(t->v);
-    if (auto t = B.get(p + "side.proj", W, sd)) L.side_proj = B.up(t->v);
+    if (auto t = B.get(p + "side.proj", W, sd)) {           // kept transposed [sd, W]: a token's row kernel reads it along the width
+      std::vector<float> tr((size_t)sd * W);
+      for (int r = 0; r < W; ++r)
+        for (int k = 0; k < sd; ++k) tr[(size_t)k * W + r] = t->v[(size_t)r * sd + k];
+      L.side_proj = B.up(tr);
+    }
     if (auto t = B.get(p + "side.norm", W, -1)) L.side_norm = B.up_f32(t->v);
   }
   if (c.ff_kind == HY_FF_NONE) return B.rc;
@@ -1689,7 +1694,8 @@ void stream_row(hy_engine* h, const Batch& b, const StreamOp& o) {
 template <typename AT>
 void canon_input(hy_engine* h, const Batch& b, const float* w, float* tails) {
   const int W = h->m.width, taps = h->m.canon_taps;
-  canon_kernel<AT><<<dim3((W + 127) / 128, b.T), 128, 0, h->stream>>>(b, h->hn, W, taps, w, tails, (AT*)h->hbuf);
+  if (W % 4 == 0) canon_kernel<AT, 4><<<dim3((W / 4 + 127) / 128, b.T), 128, 0, h->stream>>>(b, h->hn, W, taps, w, tails, (AT*)h->hbuf);
+  else canon_kernel<AT, 1><<<dim3((W + 127) / 128, b.T), 128, 0, h->stream>>>(b, h->hn, W, taps, w, tails, (AT*)h->hbuf);
   h->launches++;
   if (taps > 1) {
     conv_tail_kernel<float><<<dim3((W + 127) / 128, b.E), 128, 0, h->stream>>>(b, h->hn, W, 0, W, taps, tails);

@@ -4,7 +4,8 @@ bandwidth for decode).  Random weights, synthetic tokens.  `bench.py --compare-h
 equal width / depth / feed-forward size.  `bench.py --compare-famepel`: Famepel beside Kinetar at equal width / depth and
 equal ACTIVE feed-forward size per token (top x expert size = the dense size).  `bench.py --compare-vosolorn`: Vosolorn
 beside Famepel at equal width / depth (both are normed-sublayer designs with layer scales, a matrix-state recurrence,
-attention and routed experts)."""
+attention and routed experts).  `bench.py --compare-sebavik`: Sebavik beside Vosolorn with attention in every layer (both: windowed
+attention over paged keys and values, a gated dense feed-forward alternating with routed experts, RMS norms)."""
 from __future__ import annotations
 
 import time
@@ -162,7 +163,7 @@ def vosolorn_description(sz: dict) -> dict:
            "rot": {"base": 1e6, "dims": 64}, "scale": 128 ** -0.5}
     layers = []
     for i in range(sz["layers"]):
-        kind = "attention" if i % 4 == 2 else "mlstm"
+        kind = "attention" if i % 4 == 2 or sz.get("all_attention") else "mlstm"
         layers.append({"type": kind, "mixer": att if kind == "attention" else mem, "mlp": moe if i % 2 else dense})
     return {"architecture": "Vosolorn", "layers": layers, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "vocab": sz["vocab"], "width": W}
 
@@ -200,6 +201,75 @@ def vosolorn_weights(desc: dict, seed: int) -> Dict[str, np.ndarray]:
                 w[f"{p}mlp.e{e}.up"], w[f"{p}mlp.e{e}.down"] = lin(ff, W), lin(W, ff)
             w[p + "mlp.shared.up"], w[p + "mlp.shared.down"] = lin(mlp["shared"]["ff"], W), lin(W, mlp["shared"]["ff"])
     return w
+
+
+def sebavik_description(sz: dict) -> dict:
+    """Every layer: biased attention in heads of 128 over a window of 1024 tokens plus 64 kept first tokens, scores capped at
+    50, values blended with the first layer's; feed-forwards alternate between the clamped gated dense layer and gated
+    experts of ff / top each (8 x top of them, `top` per token); input convolutions of 4 taps, a token input of 32, a pair
+    table of 65521 buckets, depth average."""
+    W, top = sz["width"], sz.get("top", 4)
+    moe = {"kind": "moe", "expert": {"ff": sz["ff"] // top}, "router": {"experts": 8 * top, "top": top}}
+    dense = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
+    att = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": 1024, "keep_first": 64},
+           "scale": 128 ** -0.5, "softcap": 50.0, "v_mix": True}
+    layers = [{"type": "attention", "mixer": att, "mlp": moe if i % 2 else dense} for i in range(sz["layers"])]
+    return {"architecture": "Sebavik", "canon": {"taps": 4}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": layers, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "token_side": {"dim": 32}, "vocab": sz["vocab"], "width": W}
+
+
+def sebavik_weights(desc: dict, seed: int) -> Dict[str, np.ndarray]:
+    rng = np.random.default_rng(seed)
+    W, V, L = desc["width"], desc["vocab"], len(desc["layers"])
+    taps, side = desc["canon"]["taps"], desc["token_side"]["dim"]
+
+    def lin(n, k):
+        return (rng.standard_normal((n, k), dtype=np.float32) / np.sqrt(k)).astype(np.float32)
+
+    def vec(n, s=0.1, b=0.0):
+        return (rng.standard_normal(n, dtype=np.float32) * s + b).astype(np.float32)
+    w = {"embed": lin(V, W) * 4.0, "bigram": lin(desc["embedding"]["bigram"]["buckets"] + 1, W), "side.embed": lin(V, side * L) * 4.0,
+         "final.norm": vec(W, 0.1, 1.0)}
+    for i, lc in enumerate(desc["layers"]):
+        p, m, M = f"l{i}.", lc["mixer"], f"l{i}.mix."
+        H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        w.update({p + "norm1": vec(W, 0.1, 1.0), p + "ls1": vec(W, 0.1, 0.7), p + "canon1": vec((W, taps), 0.3),
+                  p + "dwa": np.concatenate([vec(i + 1, 0.1), np.ones(1, np.float32)]),
+                  M + "q": lin(H * D, W), M + "q.b": vec(H * D), M + "k": lin(G * D, W), M + "k.b": vec(G * D), M + "v": lin(G * Dv, W),
+                  M + "v.b": vec(G * Dv), M + "vmix": np.float32(0.3).reshape(()), M + "r1": vec(H, 0.1, 0.5), M + "r2": vec(H, 0.01, 0.1),
+                  M + "sink": vec(H, 1.0), M + "o": lin(W, H * Dv),
+                  p + "side.gate": lin(side, W), p + "side.proj": lin(W, side), p + "side.norm": vec(W, 0.1, 1.0)})
+        mlp = lc["mlp"]
+        w.update({p + "norm2": vec(W, 0.1, 1.0), p + "ls2": vec(W, 0.1, 0.7), p + "canon2": vec((W, taps), 0.3)})
+        if mlp["kind"] == "dense":
+            w.update({p + "mlp.gate": lin(mlp["ff"], W), p + "mlp.up": lin(mlp["ff"], W), p + "mlp.down": lin(W, mlp["ff"])})
+        else:
+            ff, E = mlp["expert"]["ff"], mlp["router"]["experts"]
+            w[p + "mlp.router"] = lin(E, W) * 2.0
+            for e in range(E):
+                w[f"{p}mlp.e{e}.gate"], w[f"{p}mlp.e{e}.up"], w[f"{p}mlp.e{e}.down"] = lin(ff, W), lin(ff, W), lin(W, ff)
+    return w
+
+
+def _sebavik_costs(desc: dict, hc, prompt: int) -> dict:
+    """Multiply-adds per token per kernel group (the dense feed-forward counts under gemm_in / gemm_out, where its products
+    run); for attention the multiply-adds of one whole prompt over the keys a position really sees."""
+    W = desc["width"]
+    per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0, "experts": 0, "expert_weights": 0, "delta": 0, "attention_prompt": 0}
+    for s in hc.layers:
+        per["gemm_in"] += (s.b_heads * s.b_dim + s.b_kv_heads * (s.b_dim + s.b_vdim)) * W
+        per["gemm_out"] += s.b_heads * s.b_vdim * W
+        win = s.b_window if s.b_window > 0 else prompt
+        seen = sum(min(i + 1, win) + min(s.b_keep_first, max(0, i + 1 - win)) for i in range(prompt))
+        per["attention_prompt"] += seen * s.b_heads * (s.b_dim + s.b_vdim)
+        if s.ff_kind == 3:
+            per["gemm_in"] += 2 * s.ff * W
+            per["gemm_out"] += s.ff * W
+        elif s.ff_kind == 2:
+            per["experts"] += s.x_top * 3 * s.ff * W
+            per["expert_weights"] += s.x_experts * 3 * s.ff * W
+    per["head"] = desc["vocab"] * W
+    return per
 
 
 def _vosolorn_costs(desc: dict, hc, prompt: int) -> dict:
@@ -260,6 +330,8 @@ def _hybrid_costs(desc: dict, hc, prompt: int = 0) -> dict:
         return _famepel_costs(desc, hc, prompt)
     if desc["architecture"] == "Vosolorn":
         return _vosolorn_costs(desc, hc, prompt)
+    if desc["architecture"] == "Sebavik":
+        return _sebavik_costs(desc, hc, prompt)
     W = desc["width"]
     per = {"gemm_in": 0, "gemm_out": 0, "small_gemm": 0}
     for s in hc.layers:
@@ -287,9 +359,12 @@ def run_hybrid(size: str, prompt: int, decode_steps: int, batches: List[int], pe
     if design == "Famepel":
         desc = famepel_description(sz)
         w = famepel_weights(desc, seed)
-    elif design == "Vosolorn":
-        desc = vosolorn_description(sz)
+    elif design in ("Vosolorn", "VosolornAttention"):
+        desc = vosolorn_description(dict(sz, all_attention=design == "VosolornAttention"))
         w = vosolorn_weights(desc, seed)
+    elif design == "Sebavik":
+        desc = sebavik_description(sz)
+        w = sebavik_weights(desc, seed)
     else:
         desc = hybrid_description(sz)
         w = hybrid_weights(desc, seed)
