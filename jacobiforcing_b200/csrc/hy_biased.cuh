@@ -185,17 +185,16 @@ __global__ void __launch_bounds__(256) stream_row_kernel(Batch b, StreamOp o, in
 }
 
 // ---- a sublayer's input: the normed row plus its causal convolution over time ------------------------------------------------------
-// hn [T, width] fp32 normed rows; w [width, taps] fp32 (last tap = the current token); state [slot][taps - 1][width] fp32 =
+// hn [T, width] fp32 normed rows; w [taps, width] fp32 (tap-major; last tap = the current token); state [slot][taps - 1][width] fp32 =
 // the request's last taps - 1 normed rows.  taps == 0: the normed row passes as it is.
 template <typename AT, int CH>
 __global__ void canon_kernel(Batch b, const float* __restrict__ hn, int width, int taps, const float* __restrict__ w,
                              const float* __restrict__ state, AT* __restrict__ out) {
+  struct alignas(4 * CH) Row { float v[CH]; };                        // CH consecutive channels per thread (width % CH == 0)
   const int t = blockIdx.y;
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * CH;         // CH consecutive channels per thread (width % CH == 0)
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * CH;
   if (c >= width) return;
-  float acc[CH];
-#pragma unroll
-  for (int k = 0; k < CH; ++k) acc[k] = hn[(size_t)t * width + c + k];
+  Row acc = *reinterpret_cast<const Row*>(hn + (size_t)t * width + c);
   if (taps > 0) {
     const int e = b.tok_ent[t];
     const int start = b.ent_start[e], pos0 = b.ent_pos0[e], j = t - start;
@@ -204,12 +203,13 @@ __global__ void canon_kernel(Batch b, const float* __restrict__ hn, int width, i
       const int src = j - (taps - 1) + i;
       const float* row = src >= 0 ? hn + (size_t)(start + src) * width : pos0 + src >= 0 ? st + (size_t)(taps - 1 + src) * width : nullptr;
       if (!row) continue;
+      const Row r = *reinterpret_cast<const Row*>(row + c), wv = *reinterpret_cast<const Row*>(w + (size_t)i * width + c);
 #pragma unroll
-      for (int k = 0; k < CH; ++k) acc[k] = fmaf(w[(size_t)(c + k) * taps + i], row[c + k], acc[k]);
+      for (int k = 0; k < CH; ++k) acc.v[k] = fmaf(wv.v[k], r.v[k], acc.v[k]);
     }
   }
 #pragma unroll
-  for (int k = 0; k < CH; ++k) out[(size_t)t * width + c + k] = from_f<AT>(acc[k]);
+  for (int k = 0; k < CH; ++k) out[(size_t)t * width + c + k] = from_f<AT>(acc.v[k]);
 }
 
 // ---- values blended with the first blending layer's; keys and values into their pages ----------------------------------------------
@@ -309,12 +309,14 @@ __global__ void __launch_bounds__(128) biased_attn_kernel(Batch b, const AT* __r
 // operands, fp32 accumulators); scale, cap, distance bias and the online softmax in fp32; O += P V with P split into a
 // bf16 head and a bf16 remainder (the weights stay 32-bit in effect).  The sink joins the denominator at the end.  Key and
 // value rows are zero-padded to DP columns in shared memory (dim, vdim multiples of 8, at most DP); key / value tiles are
-// double buffered.  tanh and the logarithm use the fast exponential / logarithm units: 1 - 2 / (exp(2 z) + 1) and
+// double buffered.  With n_splits > 1 (steps of few rows, decoding) a unit's tile list is cut into n_splits runs, each run
+// leaves (maximum, denominator, unnormalised output) per row, and biased_combine_kernel merges them with the sink.  tanh and the logarithm use the fast exponential / logarithm units: 1 - 2 / (exp(2 z) + 1) and
 // log(1 + r2 d), both far inside the rounding of the bf16 operands.
 template <int DP>
 __global__ void __launch_bounds__(128) biased_mma_kernel(Batch b, const AttnUnit* __restrict__ units, const bf16* __restrict__ q,
                                                          int ldq, BiasedCfg c, const bf16* __restrict__ kc,
-                                                         const bf16* __restrict__ vc, bf16* __restrict__ out, int ldo) {
+                                                         const bf16* __restrict__ vc, bf16* __restrict__ out, int ldo,
+                                                         int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int LD = DP + 8;                            // padded row (elements): ldmatrix rows fall into distinct banks
   extern __shared__ __align__(16) unsigned char hy_smem[];
   bf16* kbuf = reinterpret_cast<bf16*>(hy_smem);        // [2][64 * LD] key tiles: one in use, one in flight
@@ -377,12 +379,19 @@ __global__ void __launch_bounds__(128) biased_mma_kernel(Batch b, const AttnUnit
     }
     jf::cp_async_commit();
   };
-  load_tile(0);
-  for (int it = 0; it < n_tiles; ++it) {
+  // key splits (steps of few rows): split s of n walks the tiles [s per, (s + 1) per) of the unit's list
+  int it_lo = 0, it_hi = n_tiles;
+  if (n_splits > 1) {
+    const int per = (n_tiles + n_splits - 1) / n_splits;
+    it_lo = min(u.split * per, n_tiles);
+    it_hi = min(it_lo + per, n_tiles);
+  }
+  if (it_lo < it_hi) load_tile(it_lo);
+  for (int it = it_lo; it < it_hi; ++it) {
     const int j0 = tile_j0(it);
     const bf16* ks = kbuf + (it & 1) * 64 * LD;
     const bf16* vs = vbuf + (it & 1) * 64 * LD;
-    if (it + 1 < n_tiles) { load_tile(it + 1); jf::cp_async_wait_1(); }       // the next tile flies under this tile's products
+    if (it + 1 < it_hi) { load_tile(it + 1); jf::cp_async_wait_1(); }         // the next tile flies under this tile's products
     else jf::cp_async_wait_all();
     __syncthreads();
     if (warp_live) {
@@ -484,6 +493,18 @@ __global__ void __launch_bounds__(128) biased_mma_kernel(Batch b, const AttnUnit
     const int row = hh ? r_hi : r_lo;
     if (row >= rows_total) continue;
     const int t = start + row / R, h = hh ? h_hi : h_lo;
+    if (n_splits > 1) {                                  // unnormalised partial result; the combine kernel adds the sink
+      const size_t slot = ((size_t)t * c.H + h) * n_splits + u.split;
+      float* pp = part_o + slot * DP;
+#pragma unroll
+      for (int i = 0; i < DP / 8; ++i)
+        *reinterpret_cast<float2*>(pp + i * 8 + (lane & 3) * 2) = make_float2(o[i][hh * 2], o[i][hh * 2 + 1]);
+      if ((lane & 3) == 0) {
+        part_ml[slot * 2] = hh ? m_hi : m_lo;
+        part_ml[slot * 2 + 1] = hh ? l_hi : l_lo;
+      }
+      continue;
+    }
     // the sink: one more term in the denominator
     const float m = hh ? m_hi : m_lo, sk = c.sink[h];
     const float top = fmaxf(m, sk);
@@ -496,6 +517,26 @@ __global__ void __launch_bounds__(128) biased_mma_kernel(Batch b, const AttnUnit
       if (d >= c.vdim) continue;
       *reinterpret_cast<__nv_bfloat162*>(po + d) = __floats2bfloat162_rn(o[i][hh * 2] * inv, o[i][hh * 2 + 1] * inv);
     }
+  }
+}
+
+// Merge the key splits of one (token, head) with the sink: one block per (token, head).  A split without keys holds a
+// maximum of -inf and a denominator of zero.  part_o rows are pstride wide.
+template <typename OT>
+__global__ void biased_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
+                                      int H, int vdim, int pstride, int n_splits, OT* __restrict__ out, int ldo) {
+  const int t = blockIdx.x / H, h = blockIdx.x % H;
+  const size_t slot0 = ((size_t)t * H + h) * n_splits;
+  const float sk = sink[h];
+  float M = sk;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
+  float L = expf(sk - M);
+  for (int s = 0; s < n_splits; ++s) L += part_ml[(slot0 + s) * 2 + 1] * expf(part_ml[(slot0 + s) * 2] - M);
+  const float inv = 1.0f / L;
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < n_splits; ++s) acc += part_o[(slot0 + s) * pstride + d] * expf(part_ml[(slot0 + s) * 2] - M);
+    out[(size_t)t * ldo + h * vdim + d] = from_f<OT>(acc * inv);
   }
 }
 

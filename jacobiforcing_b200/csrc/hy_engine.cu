@@ -134,7 +134,7 @@ struct hy_engine {
   // tensor-core attention: work units of the step (per head layout), partial results per (row, key split)
   AttnUnit* units_d = nullptr; AttnUnit* units_h = nullptr; size_t units_cap = 0; int units_n = 0;
   int units_H = 0, units_G = 0, units_split = 0, units_ns = 0;
-  float* part_o = nullptr; float* part_ml = nullptr; size_t part_rows = 0;
+  float* part_o = nullptr; float* part_ml = nullptr; size_t part_rows = 0, part_dim = 0;
   const int32_t* step_start = nullptr; const int32_t* step_pos0 = nullptr;     // host views of the running step
   size_t esz() const { return m.dtype == HY_DTYPE_F32 ? 4 : 2; }
 };
@@ -742,6 +742,14 @@ int finalize_postnorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
   return B.rc;
 }
 
+// [width, taps] -> [taps, width]: the convolution kernel reads a tap's weights along the width
+std::vector<float> tap_major(const std::vector<float>& w, int W, int taps) {
+  std::vector<float> o((size_t)W * taps);
+  for (int c = 0; c < W; ++c)
+    for (int i = 0; i < taps; ++i) o[(size_t)i * W + c] = w[(size_t)c * taps + i];
+  return o;
+}
+
 // One layer of a pre-norm model: norms, layer scales, input convolutions with their tails, the biased attention's merged
 // projection with its bias, pages for keys and values, the feed-forward, the token input and the depth average's weights.
 int finalize_prenorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
@@ -761,7 +769,7 @@ int finalize_prenorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
   if (auto t = B.get(p + "norm1", W, -1)) L.pn1 = B.up_f32(t->v);
   if (auto t = B.get(p + "ls1", W, -1)) L.ls1 = B.up_f32(t->v);
   if (taps > 0) {
-    if (auto t = B.get(p + "canon1", W, taps)) L.canon1 = B.up_f32(t->v);
+    if (auto t = B.get(p + "canon1", W, taps)) L.canon1 = B.up_f32(tap_major(t->v, W, taps));
     if (dev_alloc(h, (void**)&L.conv_state, (size_t)rt.num_slots * (taps - 1) * W * 4, &h->bytes_state)) return HY_ERR_CUDA;
   }
   if (h->m.depth_avg) { if (auto t = B.get(p + "dwa", (int64_t)i + 2, -1)) L.dwa = B.up_f32(t->v); }
@@ -812,7 +820,7 @@ int finalize_prenorm_layer(hy_engine* h, Builder& B, size_t i, Maxima& mx) {
   if (auto t = B.get(p + "norm2", W, -1)) L.pn2 = B.up_f32(t->v);
   if (auto t = B.get(p + "ls2", W, -1)) L.ls2 = B.up_f32(t->v);
   if (taps > 0) {
-    if (auto t = B.get(p + "canon2", W, taps)) L.canon2 = B.up_f32(t->v);
+    if (auto t = B.get(p + "canon2", W, taps)) L.canon2 = B.up_f32(tap_major(t->v, W, taps));
     if (dev_alloc(h, (void**)&L.conv_state2, (size_t)rt.num_slots * (taps - 1) * W * 4, &h->bytes_state)) return HY_ERR_CUDA;
   }
   if (c.ff_kind == HY_FF_GATED) return load_gated_dense(h, B, L, c, p, mx);
@@ -991,7 +999,10 @@ extern "C" int hy_finalize(hy_handle h) {
     for (auto& c : h->lc) {
       if (c.mixer == HY_MIX_ATTN_SCAN) { maxH = std::max(maxH, c.a_heads); maxG = std::max(maxG, c.a_kv_heads); maxD = std::max(maxD, c.a_dim); }
       if (c.mixer == HY_MIX_WINDOW) { maxH = std::max(maxH, c.w_heads); maxG = std::max(maxG, c.w_kv_heads); maxD = std::max(maxD, 8); }
-      if (c.mixer == HY_MIX_BIASED) { maxH = std::max(maxH, c.b_heads); maxG = std::max(maxG, c.b_kv_heads); maxD = std::max(maxD, 8); }
+      if (c.mixer == HY_MIX_BIASED) {                       // partial rows of the key splits are one tile row wide
+        maxH = std::max(maxH, c.b_heads); maxG = std::max(maxG, c.b_kv_heads);
+        maxD = std::max(maxD, (c.b_dim <= 64 && c.b_vdim <= 64) ? 64 : 128);
+      }
       if (c.mixer == HY_MIX_LATENT) {
         maxH = std::max(maxH, c.l_heads); maxG = std::max(maxG, 1);
         maxD = std::max(maxD, std::max(c.l_kv_rank + c.l_rot_dim, c.l_kv_rank <= 128 ? 128 : c.l_kv_rank <= 256 ? 256 : 512));
@@ -999,6 +1010,7 @@ extern "C" int hy_finalize(hy_handle h) {
     }
     if (maxH > 0) {
       h->part_rows = std::max<size_t>(T * maxH, 4096);
+      h->part_dim = (size_t)maxD;
       h->units_cap = h->part_rows / 64 + (size_t)rt.max_step_entries * maxG * 257 + 64;
       if (dev_alloc(h, (void**)&h->part_o, h->part_rows * maxD * 4, &h->bytes_ws)) return HY_ERR_CUDA;
       if (dev_alloc(h, (void**)&h->part_ml, h->part_rows * 2 * 4, &h->bytes_ws)) return HY_ERR_CUDA;
@@ -1146,6 +1158,42 @@ bool window_units(hy_engine* h, int E, int H, int G) {
   }
   cudaMemcpyAsync(h->units_d, h->units_h, n * sizeof(AttnUnit), cudaMemcpyHostToDevice, h->stream);
   h->units_n = (int)n; h->units_H = H; h->units_G = G; h->units_split = -1; h->units_ns = 1;
+  return true;
+}
+
+// Work units of the tensor-core biased attention: (entry, key head, tile of 64 rows, key split).  Steps of few rows whose
+// requests see many key tiles (decoding) cut every unit's tile list into n splits so that the SMs have work; prompts run
+// unsplit.  The number of splits depends on the step only, a row's result on it only within rounding.
+bool biased_units(hy_engine* h, int E, int T, int H, int G, int window, int keep, int dp) {
+  const int R = H / G;
+  if (h->units_n > 0 && h->units_H == H && h->units_G == G && h->units_split == -2 - window) return true;
+  if (h->units_n > 0) cudaStreamSynchronize(h->stream);        // another layout earlier in this step still reads the list
+  int units0 = 0, max_tiles = 1;
+  for (int e = 0; e < E; ++e) {
+    const int cnt = h->step_start[e + 1] - h->step_start[e], last = h->step_pos0[e] + cnt - 1;
+    units0 += G * ((cnt * R + 63) / 64);
+    const int seen = window > 0 ? std::min(last + 1, window + keep) : last + 1;
+    max_tiles = std::max(max_tiles, seen / 64 + 2);
+  }
+  int ns = 1;
+  if (units0 * 2 <= 148 && max_tiles >= 4 && h->part_o) {
+    ns = std::min(std::min(148 / units0, (max_tiles + 1) / 2), 64);
+    ns = (int)std::min<size_t>((size_t)ns, h->part_rows / ((size_t)T * H));
+    if ((size_t)dp > h->part_dim) ns = 1;
+    ns = std::max(ns, 1);
+  }
+  size_t n = 0;
+  for (int e = 0; e < E; ++e) {
+    const int rows = (h->step_start[e + 1] - h->step_start[e]) * R;
+    for (int g = 0; g < G; ++g)
+      for (int row0 = (rows - 1) / 64 * 64; row0 >= 0; row0 -= 64)
+        for (int sp = 0; sp < ns; ++sp) {
+          if (n >= h->units_cap) return false;
+          h->units_h[n++] = AttnUnit{e, g, row0, sp};
+        }
+  }
+  cudaMemcpyAsync(h->units_d, h->units_h, n * sizeof(AttnUnit), cudaMemcpyHostToDevice, h->stream);
+  h->units_n = (int)n; h->units_H = H; h->units_G = G; h->units_split = -2 - window; h->units_ns = ns;
   return true;
 }
 
@@ -1738,7 +1786,7 @@ int prenorm_layer(hy_engine* h, const Batch& b, size_t li) {
     if constexpr (std::is_same<AT, bf16>::value) {
       static const bool simt_only = getenv("HY_BIASED_SIMT") != nullptr;      // developer switch
       if (!simt_only && c.b_dim % 8 == 0 && c.b_vdim % 8 == 0 && c.b_dim <= 128 && c.b_vdim <= 128 && h->ld_pin % 8 == 0 && h->units_d &&
-          window_units(h, E, c.b_heads, c.b_kv_heads)) {
+          biased_units(h, E, T, c.b_heads, c.b_kv_heads, c.b_window, c.b_keep_first, (c.b_dim <= 64 && c.b_vdim <= 64) ? 64 : 128)) {
         tc = true;
         static bool attr = false;
         if (!attr) {
@@ -1748,10 +1796,15 @@ int prenorm_layer(hy_engine* h, const Batch& b, size_t li) {
         }
         if (c.b_dim <= 64 && c.b_vdim <= 64)
           biased_mma_kernel<64><<<h->units_n, 128, window_mma_smem(64), s>>>(b, h->units_d, pin + L.c_q, h->ld_pin, bc, (const bf16*)L.cache,
-                                                                            (const bf16*)L.cache_v, cat, h->ld_cat);
+                                                                            (const bf16*)L.cache_v, cat, h->ld_cat, h->units_ns, h->part_o, h->part_ml);
         else
           biased_mma_kernel<128><<<h->units_n, 128, window_mma_smem(128), s>>>(b, h->units_d, pin + L.c_q, h->ld_pin, bc, (const bf16*)L.cache,
-                                                                              (const bf16*)L.cache_v, cat, h->ld_cat);
+                                                                              (const bf16*)L.cache_v, cat, h->ld_cat, h->units_ns, h->part_o, h->part_ml);
+        if (h->units_ns > 1) {
+          biased_combine_kernel<bf16><<<T * c.b_heads, 64, 0, s>>>(h->part_o, h->part_ml, L.b_sink, c.b_heads, c.b_vdim,
+                                                                   (c.b_dim <= 64 && c.b_vdim <= 64) ? 64 : 128, h->units_ns, cat, h->ld_cat);
+          h->launches++;
+        }
       }
     }
     if (!tc)
