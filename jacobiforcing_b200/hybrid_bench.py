@@ -205,17 +205,17 @@ def vosolorn_weights(desc: dict, seed: int) -> Dict[str, np.ndarray]:
 
 def sebavik_description(sz: dict) -> dict:
     """Every layer: biased attention in heads of 128 over a window of 1024 tokens plus 64 kept first tokens, scores capped at
-    50, values blended with the first layer's; feed-forwards alternate between the clamped gated dense layer and gated
+    30, values blended with the first layer's; feed-forwards alternate between the clamped gated dense layer and gated
     experts of ff / top each (8 x top of them, `top` per token); input convolutions of 4 taps, a token input of 32, a pair
     table of 65521 buckets, depth average."""
     W, top = sz["width"], sz.get("top", 4)
     moe = {"kind": "moe", "expert": {"ff": sz["ff"] // top}, "router": {"experts": 8 * top, "top": top}}
     dense = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
     att = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": 1024, "keep_first": 64},
-           "scale": 128 ** -0.5, "softcap": 50.0, "v_mix": True}
+           "scale": 128 ** -0.5, "softcap": 30.0, "v_mix": True}
     layers = [{"type": "attention", "mixer": att, "mlp": moe if i % 2 else dense} for i in range(sz["layers"])]
-    return {"architecture": "Sebavik", "canon": {"taps": 4}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
-            "layers": layers, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "token_side": {"dim": 32}, "vocab": sz["vocab"], "width": W}
+    return {"architecture": "Sebavik", "canon": {"taps": 4}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 53, "mul_cur": 29}},
+            "layers": layers, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "token_side": {"dim": 32}, "vocab": sz["vocab"], "width": W}
 
 
 def sebavik_weights(desc: dict, seed: int) -> Dict[str, np.ndarray]:

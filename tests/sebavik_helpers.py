@@ -30,7 +30,7 @@ def attn(heads=4, kv_heads=2, dim=16, vdim=12, size=11, keep=3, scale=0.35, cap=
     return {"type": "attention", "mixer": m, "mlp": dense() if mlp == "default" else mlp}
 
 
-def model_config(layers, width=40, vocab=70, emb_scale=2.0, mult=0.6, taps=3, side=5, buckets=37, eps=1e-5):
+def model_config(layers, width=40, vocab=70, emb_scale=2.0, mult=0.6, taps=4, side=5, buckets=37, eps=2e-5):
     cfg = {"architecture": "Sebavik", "embedding": {"scale": emb_scale}, "layers": copy.deepcopy(layers), "norm": {"eps": eps},
            "residual_mult": mult, "vocab": vocab, "width": width}
     if taps:
@@ -83,7 +83,7 @@ def run(config, tokens, dtype="float32", cuts=None, seed=0, weights=None, **kw):
     return got, oracle_logits(config, w, tokens)
 
 
-def needle_model(size=24, keep=5, dim=32, vdim=16, heads=2, kv_heads=1, width=64, scale=1.0, cap=30.0, taps=3):
+def needle_model(size=24, keep=5, dim=32, vdim=16, heads=2, kv_heads=1, width=64, scale=1.0, cap=30.0, taps=4):
     """One attention layer in which token 61 asks for token 60.  The stream's first quarter is a token's key address, the
     second quarter its query address, the second half its content.  Only token 60 has a key address, so every other key
     is zero and scores zero (less its distance bias); token 61's query address is token 60's key address, so that key

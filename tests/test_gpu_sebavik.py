@@ -34,7 +34,7 @@ def test_mechanism_alone(which, dtype):
 
 
 @pytest.mark.parametrize("kw", [dict(experts=8, top=3), dict(experts=1, top=1), dict(experts=5, top=5, ff=8),
-                                dict(experts=40, top=2, ff=9), dict(experts=16, top=3, ff=64)])
+                                dict(experts=40, top=2, ff=9), dict(experts=12, top=3, ff=48)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_router_shapes(kw, dtype):
     """One expert, every expert chosen, more experts than a warp, expert sizes that the tensor-core product does not take
@@ -281,11 +281,11 @@ OTHER = [
                   attn(heads=3, kv_heads=1, dim=6, vdim=1, size=2, keep=1, mlp=dense(8, 1.0))], width=24, vocab=50, taps=1, side=1,
                  buckets=1, mult=1.0),
     # key heads == query heads, head sizes the tensor-core attention takes with its wider tile, many experts of a size the
-    # tensor-core product takes, four taps, the first layer does not blend
+    # tensor-core product takes, three taps, the first layer does not blend
     model_config([attn(heads=4, kv_heads=4, dim=24, vdim=40, size=13, keep=2, v_mix=False, mlp=moe(experts=16, top=4, ff=32)),
                   attn(heads=4, kv_heads=2, dim=72, vdim=104, size=30, keep=0, mlp=dense(64, 2.0)),
-                  attn(heads=2, kv_heads=2, dim=128, vdim=104, size=50, keep=7, mlp=None)], width=72, vocab=130, taps=4, side=16,
-                 buckets=1021, eps=1e-6, mult=0.25),
+                  attn(heads=2, kv_heads=2, dim=128, vdim=104, size=50, keep=7, mlp=None)], width=72, vocab=130, taps=3, side=12,
+                 buckets=509, eps=1e-6, mult=0.25),
     # sizes that are not multiples of 8 anywhere, head sizes beyond a warp, two taps, no pair table, no token input
     model_config([attn(heads=6, kv_heads=2, dim=20, vdim=70, size=9, keep=4, mlp=moe(experts=3, top=2, ff=13)),
                   attn(heads=1, kv_heads=1, dim=136, vdim=33, size=100, keep=0, cap=None, v_mix=False, mlp=dense(27, 0.5)),

@@ -18,7 +18,7 @@ def test_config_reader_reads_every_size_and_constant():
     hc = HybridConfig.from_dict(SMALL)
     assert (hc.architecture, hc.width, hc.vocab, len(hc.layers)) == ("Sebavik", 40, 70, 5)
     assert (hc.block_kind, hc.norm_kind, hc.pos_kind, hc.tied_head) == (hcfg.BLOCK_PRENORM, hcfg.NORM_RMS, hcfg.POS_NONE, True)
-    assert (hc.resid_mult, hc.canon_taps, hc.side_dim, hc.depth_avg) == (0.6, 3, 5, 1)
+    assert (hc.resid_mult, hc.canon_taps, hc.side_dim, hc.depth_avg) == (0.6, 4, 5, 1)
     assert (hc.pair_buckets, hc.pair_mul_prev, hc.pair_mul_cur, hc.emb_scale) == (37, 13, 7, 2.0)
     a = hc.layers[3]
     assert (a.mixer, a.b_heads, a.b_kv_heads, a.b_dim, a.b_vdim, a.b_window, a.b_keep_first, a.b_v_mix) == (hcfg.MIX_BIASED, 6, 2, 24, 12, 19, 9, 1)
