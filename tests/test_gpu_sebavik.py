@@ -11,8 +11,8 @@ import pytest
 import torch
 
 from oracle import sebavik_plain as plain
-from tests.sebavik_helpers import (SMALL, TOL, Harness, attn, close, dense, model_config, moe, needle_model, needle_tokens,
-                                   oracle_logits, rand_tokens, rel_err, run)
+from tests.sebavik_helpers import (SMALL, TOL, Harness, attn, close, dense, model_config, moe, near_ties, needle_model,
+                                   needle_tokens, oracle_logits, rand_tokens, rel_err, run)
 
 pytestmark = pytest.mark.gpu
 
@@ -38,11 +38,15 @@ def test_mechanism_alone(which, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_router_shapes(kw, dtype):
     """One expert, every expert chosen, more experts than a warp, expert sizes that the tensor-core product does not take
-    and ones it takes; many tokens so that the expert-sorted path runs, few so that the per-pair one does."""
+    and ones it takes; many tokens so that the expert-sorted path runs, few so that the per-pair one does.  The router's
+    weights are made three times larger so that near ties between the last chosen and the first rejected expert are rare."""
     cfg = model_config([attn(heads=1, kv_heads=1, dim=8, vdim=8, mlp=moe(**kw)), attn(heads=2, kv_heads=1, dim=8, vdim=8, mlp=moe(**kw))])
+    w = plain.random_weights(cfg, 0)
+    for i in range(2):
+        w[f"l{i}.mlp.router"] = (w[f"l{i}.mlp.router"].float() * 3.0).to(torch.bfloat16)
     toks = rand_tokens(80, cfg["vocab"], 4)
-    got, want = run(cfg, toks, dtype, cuts=[60, 1, 7, 1])
-    assert close(got, want, dtype)
+    got, want = run(cfg, toks, dtype, cuts=[60, 1, 7, 1], weights=w)
+    assert close(got, want, dtype, near_ties(cfg, w, toks) if dtype == "bfloat16" else ())
 
 
 def _edit(cfg, w, what):
@@ -101,8 +105,9 @@ def test_prefill_equals_token_by_token(dtype):
     toks = rand_tokens(70, SMALL["vocab"], 5)
     whole, want = run(SMALL, toks, dtype)
     single, _ = run(SMALL, toks, dtype, cuts=[1])
-    assert close(whole, want, dtype)
-    assert close(single, want, dtype)
+    skip = near_ties(SMALL, plain.random_weights(SMALL, 0), toks) if dtype == "bfloat16" else ()
+    assert close(whole, want, dtype, skip)
+    assert close(single, want, dtype, skip)
     if dtype == "float32":
         assert close(single, whole)
 
@@ -157,7 +162,8 @@ def test_mixed_batches_and_reuse(dtype):
     finally:
         hz.close()
     for k in reqs:
-        assert close(np.concatenate(got[k], 0), ref[k], dtype), k
+        skip = near_ties(SMALL, w, reqs[k]) if dtype == "bfloat16" else ()
+        assert close(np.concatenate(got[k], 0), ref[k], dtype, skip), k
 
 
 def test_slot_and_pages_used_again_start_from_the_empty_state():
@@ -271,7 +277,7 @@ def test_long_decoding():
     got, want = run(SMALL, toks, "float32", cuts=[4, 1], num_pages=20)
     assert close(got, want)
     got16, _ = run(SMALL, toks, "bfloat16", cuts=[4, 1], num_pages=20)
-    assert close(got16, want, "bfloat16")
+    assert close(got16, want, "bfloat16", near_ties(SMALL, plain.random_weights(SMALL, 0), toks))
 
 
 OTHER = [
@@ -299,7 +305,7 @@ def test_other_sizes(idx, dtype):
     cfg = OTHER[idx]
     toks = rand_tokens(60, cfg["vocab"], 60 + idx)
     got, want = run(cfg, toks, dtype, cuts=[21, 3, 1], page_size=32, num_pages=4)
-    assert close(got, want, dtype)
+    assert close(got, want, dtype, near_ties(cfg, plain.random_weights(cfg, 0), toks) if dtype == "bfloat16" else ())
 
 
 # ---- greedy generation through the engine's own entry points ------------------------------------------------------------------------
