@@ -294,7 +294,7 @@ OTHER = [
                  buckets=509, eps=1e-6, mult=0.25),
     # sizes that are not multiples of 8 anywhere, head sizes beyond a warp, two taps, no pair table, no token input
     model_config([attn(heads=6, kv_heads=2, dim=20, vdim=70, size=9, keep=4, mlp=moe(experts=3, top=2, ff=13)),
-                  attn(heads=1, kv_heads=1, dim=136, vdim=33, size=100, keep=0, cap=None, v_mix=False, mlp=dense(27, 0.5)),
+                  attn(heads=1, kv_heads=1, dim=144, vdim=33, size=100, keep=0, cap=None, v_mix=False, mlp=dense(27, 0.5)),
                   attn(heads=2, kv_heads=2, dim=9, vdim=70, size=None, mlp=None)], width=44, vocab=61, taps=2, side=0, buckets=0),
 ]
 
